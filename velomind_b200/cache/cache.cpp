@@ -68,7 +68,7 @@ PageBook::PageBook(const CacheNeed& need_, int n_pages_, int max_slots_, int max
       table_(static_cast<size_t>(max_slots_) * max_blocks_, -1) {
     if (need.kind != CacheNeed::All && need.kind != CacheNeed::Window) throw CacheError("a cache group holds keys and values; a need of kind 'none' has none");
     if (need.kind == CacheNeed::Window && need.window <= 0) throw CacheError("a window group needs window > 0");
-    if (need.key_dim != need.value_dim)
+    if (need.value_dim != 0 && need.key_dim != need.value_dim)      // value_dim 0: one row per token and no second one (a latent that serves as both)
         throw CacheError(format("a cache group stores keys and values of one head size; a mixer asked for keys of %d and values of %d", need.key_dim,
                                 need.value_dim));
 }
@@ -224,7 +224,7 @@ SequenceCache::SequenceCache(const std::vector<CacheNeed>& needs, const std::vec
         GroupStorage s;
         s.layer_bytes = static_cast<size_t>(book.n_pages) * need.kv_heads * VM_PAGE_TOKENS * need.key_dim * dtype_size(dtype);
         s.k = std::make_unique<DeviceBuffer>(s.layer_bytes * book.layers_in_group[g], /*zero=*/true);
-        s.v = std::make_unique<DeviceBuffer>(s.layer_bytes * book.layers_in_group[g], /*zero=*/true);
+        if (need.value_dim > 0) s.v = std::make_unique<DeviceBuffer>(s.layer_bytes * book.layers_in_group[g], /*zero=*/true);
         storage.push_back(std::move(s));
     }
     state.resize(needs.size());
@@ -251,6 +251,9 @@ int SequenceCache::open() {
 }
 
 void* SequenceCache::k_pages(int group, int layer) const { return static_cast<char*>(storage[group].k->ptr) + storage[group].layer_bytes * layer; }
-void* SequenceCache::v_pages(int group, int layer) const { return static_cast<char*>(storage[group].v->ptr) + storage[group].layer_bytes * layer; }
+void* SequenceCache::v_pages(int group, int layer) const {
+    if (!storage[group].v) return nullptr;         // a group that keeps one row per token
+    return static_cast<char*>(storage[group].v->ptr) + storage[group].layer_bytes * layer;
+}
 
 }  // namespace vmb

@@ -318,9 +318,11 @@ std::vector<std::string> registered_architectures() {
 
 std::string architecture_name(const json::Value& config, const std::string& where) {
     const json::Value* a = config.find("architectures");
-    if (!a || !a->is_array() || a->as_array().empty() || !a->as_array()[0].is_string())
-        throw ConfigError(where + ": missing required key 'architectures' (a list whose first entry names the model class)");
-    return a->as_array()[0].as_string();
+    if (a && a->is_array() && !a->as_array().empty() && a->as_array()[0].is_string()) return a->as_array()[0].as_string();
+    // a configuration that names its one model class directly
+    const json::Value* one = config.find("architecture");
+    if (one && one->is_string() && !a) return one->as_string();
+    throw ConfigError(where + ": missing required key 'architectures' (a list whose first entry names the model class; 'architecture', a name, is accepted too)");
 }
 
 const PlanFunction& resolve_architecture(const json::Value& config, const std::string& where) {

@@ -249,6 +249,39 @@ VM_API int vm_swiglu(const void* gate_up, void* out, int T, int I, int act_dtype
     return vm_launch_status();
 }
 
+// ---------------------------------------------------------------- gated unit with a chosen activation: act(gate) * up
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); float32 arithmetic, one rounding at the store.
+__device__ __forceinline__ float vm_activate(float z, int kind) {
+    if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+    return z / (1.0f + expf(-z));
+}
+
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gu, T* __restrict__ out, int T_, int I, int kind) {
+    const size_t n = (size_t)T_ * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        out[idx] = vm_from_float<T>(vm_activate(vm_to_float(gu[t * 2 * I + i]), kind) * vm_to_float(gu[t * 2 * I + I + i]));
+    }
+}
+
+VM_API int vm_gated_activation(const void* gate_up, void* out, int T, int I, int kind, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (kind == VM_ACT_SILU) return vm_swiglu(gate_up, out, T, I, act_dtype, stream);
+    if (kind != VM_ACT_GELU_TANH && kind != VM_ACT_RELU_SQUARED) return VM_ERR_UNSUPPORTED;
+    const size_t n = (size_t)T * I;
+    const int threads = 256;
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (act_dtype == VM_F32) gated_activation_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, T, I, kind);
+    else if (act_dtype == VM_BF16)
+        gated_activation_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, T, I, kind);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
 // ---------------------------------------------------------------- dtype conversion (mixed-precision edges)
 template <typename A, typename B>
 __global__ void convert_kernel(const A* __restrict__ in, B* __restrict__ out, size_t n) {

@@ -1,0 +1,213 @@
+// A routed feed-forward (mixture of experts) for few tokens: every token streams the weight rows of ITS experts.
+//
+//   z = W_router x + b                      float32 logits; the `top` largest are chosen (the lowest index wins a tie)
+//   w = softmax over the chosen logits only
+//   y = sum_k w_k  W_down[e_k] act(W_up[e_k] x)   (+ s * W_down_shared act(W_up_shared x),  s = sigmoid(w_sg . x))
+//
+// Three launches: the router (a block per token), the up-projections with their activation (a warp per row of the token's
+// virtual matrix [top * ff + ff_shared, hidden]), the down-projections with the weighted sum (a warp per output column; the
+// experts are added in the order of their rank, so a token's result does not depend on the batch it is in).
+// Experts have no biases.  Weights are float32 or bfloat16 (template W), activations float32 or bfloat16 (template T);
+// all sums are float32.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float expert_act(float z, int kind) {
+    if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
+// dot product of a weight row with a float32 vector in shared memory, summed over a warp
+template <typename W> __device__ __forceinline__ float warp_dot(const W* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    for (int i = lane; i < n; i += 32) acc = fmaf(vm_to_float(w[i]), x[i], acc);
+    return vm_warp_sum(acc);
+}
+template <> __device__ __forceinline__ float warp_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        const uint4* w8 = reinterpret_cast<const uint4*>(w);
+        for (int i = lane; i < n / 8; i += 32) {
+            const uint4 p = w8[i];
+            const unsigned u[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+                acc = fmaf(__low2float(b), x[i * 8 + 2 * k], acc);
+                acc = fmaf(__high2float(b), x[i * 8 + 2 * k + 1], acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc = fmaf(__bfloat162float(w[i]), x[i], acc);
+    }
+    return vm_warp_sum(acc);
+}
+
+// ------------------------------------------------------------------------------------------------ router
+// Router weights, bias and the shared expert's gate row are float32 (exact copies of what the checkpoint stores).
+template <typename T>
+__global__ void router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ b_router,
+                              const float* __restrict__ w_gate, int hidden, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
+                              float* __restrict__ shared_gate) {
+    extern __shared__ float sm[];          // [hidden] input, [E] logits
+    float* xs = sm;
+    float* z = sm + hidden;
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(x[(size_t)t * hidden + i]);
+    __syncthreads();
+    for (int e = warp; e < E + (w_gate ? 1 : 0); e += nw) {
+        if (e < E) {
+            const float d = warp_dot<float>(w_router + (size_t)e * hidden, xs, hidden, lane);
+            if (lane == 0) z[e] = d + (b_router ? b_router[e] : 0.f);
+        } else {
+            const float d = warp_dot<float>(w_gate, xs, hidden, lane);
+            if (lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-d));
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // `top` rounds of arg-max over the logits not yet taken; the lowest index wins a tie
+        float first = 0.f, sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = z[e];
+                if (v > best) { best = v; at = e; }     // ascending e: the first maximum stays
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (k == 0) first = best;
+            const float p = expf(best - first);          // the largest chosen logit is the softmax's reference
+            sum += p;
+            if (lane == 0) {
+                chosen[(size_t)t * top + k] = at;
+                weight[(size_t)t * top + k] = p;
+                z[at] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        const float inv = 1.0f / sum;
+        for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= inv;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ up-projections
+// grid (row tiles, T); a warp per row r of the token's [top * ff + ff_shared] rows
+template <typename T, typename W>
+__global__ void experts_up_kernel(const T* __restrict__ x, const W* __restrict__ w_up, const W* __restrict__ w_up_shared,
+                                  const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared,
+                                  T* __restrict__ act) {
+    extern __shared__ float xs[];          // [hidden]
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(x[(size_t)t * hidden + i]);
+    __syncthreads();
+    const int rows = top * ff + ff_shared;
+    const int r = blockIdx.x * nw + warp;
+    if (r >= rows) return;
+    const W* wrow;
+    int kind;
+    if (r < top * ff) {
+        const int e = chosen[(size_t)t * top + r / ff];
+        wrow = w_up + ((size_t)e * ff + r % ff) * hidden;
+        kind = act_kind;
+    } else {
+        wrow = w_up_shared + (size_t)(r - top * ff) * hidden;
+        kind = act_kind_shared;
+    }
+    const float d = warp_dot<W>(wrow, xs, hidden, lane);
+    if (lane == 0) act[(size_t)t * rows + r] = vm_from_float<T>(expert_act(d, kind));
+}
+
+// ------------------------------------------------------------------------------------------------ down-projections
+// grid (column tiles, T); a warp per output column
+template <typename T, typename W>
+__global__ void experts_down_kernel(const T* __restrict__ act, const W* __restrict__ w_down, const W* __restrict__ w_down_shared,
+                                    const int* __restrict__ chosen, const float* __restrict__ weight, const float* __restrict__ shared_gate,
+                                    int hidden, int ff, int ff_shared, int top, T* __restrict__ out) {
+    extern __shared__ float as[];          // [top * ff + ff_shared]
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int rows = top * ff + ff_shared;
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) as[i] = vm_to_float(act[(size_t)t * rows + i]);
+    __syncthreads();
+    const int c = blockIdx.x * nw + warp;
+    if (c >= hidden) return;
+    float y = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = chosen[(size_t)t * top + k];
+        y = fmaf(weight[(size_t)t * top + k], warp_dot<W>(w_down + ((size_t)e * hidden + c) * ff, as + k * ff, ff, lane), y);
+    }
+    if (ff_shared > 0) {
+        const float d = warp_dot<W>(w_down_shared + (size_t)c * ff_shared, as + top * ff, ff_shared, lane);
+        y = fmaf(shared_gate ? shared_gate[t] : 1.0f, d, y);
+    }
+    if (lane == 0) out[(size_t)t * hidden + c] = vm_from_float<T>(y);
+}
+
+template <typename T, typename W>
+int launch_experts(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared, const int* chosen,
+                   const float* weight, const float* shared_gate, int T_, int hidden, int ff, int ff_shared, int top, int act_kind,
+                   int act_kind_shared, void* act, void* out, cudaStream_t stream) {
+    const int rows = top * ff + ff_shared;
+    const int warps = 8;
+    if ((size_t)hidden * sizeof(float) > 48 * 1024 || (size_t)rows * sizeof(float) > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + warps - 1) / warps, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, (const T*)x,
+                  (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, (T*)act);
+    int st = vm_launch_status();
+    if (st) return st;
+    vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + warps - 1) / warps, T_), dim3(warps * 32), (size_t)rows * sizeof(float), stream,
+                  (const T*)act, (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, (T*)out);
+    return vm_launch_status();
+}
+
+}  // namespace
+
+// chosen int32 [T, top], weight float32 [T, top], shared_gate float32 [T] (written only if w_gate is given)
+VM_API int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
+                            int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || hidden <= 0) return VM_ERR_BAD_ARG;
+    const size_t smem = (size_t)(hidden + E) * sizeof(float);
+    if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    if (act_dtype == VM_F32)
+        vm_launch_pdl(router_kernel<float>, dim3(T), dim3(128), smem, stream, (const float*)x, w_router, b_router, w_gate, hidden, E, top, chosen, weight,
+                      shared_gate);
+    else if (act_dtype == VM_BF16)
+        vm_launch_pdl(router_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, (const __nv_bfloat16*)x, w_router, b_router, w_gate, hidden, E, top,
+                      chosen, weight, shared_gate);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
+// x, out [T, hidden] and the scratch `act` [T, top * ff + ff_shared] in the activation dtype; expert weights stacked:
+// w_up [E * ff, hidden], w_down [E * hidden, ff]; the shared expert's w_up_shared [ff_shared, hidden], w_down_shared [hidden, ff_shared]
+// (ff_shared 0: none).  weight_dtype is the experts' (and the shared expert's) storage.
+VM_API int vm_experts_few_tokens(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared,
+                                 int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
+                                 int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, int act_dtype,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hidden <= 0 || ff <= 0 || ff_shared < 0 || top <= 0) return VM_ERR_BAD_ARG;
+    if (act_dtype == VM_F32 && weight_dtype == VM_F32)
+        return launch_experts<float, float>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared, top,
+                                            act_kind, act_kind_shared, act, out, stream);
+    if (act_dtype == VM_BF16 && weight_dtype == VM_BF16)
+        return launch_experts<__nv_bfloat16, __nv_bfloat16>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff,
+                                                            ff_shared, top, act_kind, act_kind_shared, act, out, stream);
+    if (act_dtype == VM_BF16 && weight_dtype == VM_F32)
+        return launch_experts<__nv_bfloat16, float>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared,
+                                                    top, act_kind, act_kind_shared, act, out, stream);
+    return VM_ERR_UNSUPPORTED;
+}

@@ -364,6 +364,24 @@ void linear_residual(const void* x, long long ldx, const DeviceTensor& W, float*
     if (switches().sync) cuda_check(cudaStreamSynchronize(s), "linear_residual");
 }
 
+void linear_batched(const void* x, long long ldx, long long stride_x, const void* W, long long stride_w, bool w_is_k_by_n, void* out, long long ldo,
+                    long long stride_o, DType dtype, int T, int N, int K, int batch, cudaStream_t s) {
+    if (T <= 0 || batch <= 0) return;
+    Timed t("linear_batched", s);
+    Blas& b = blas();
+    const cudaDataType_t ty = dtype == DType::F32 ? CUDA_R_32F : CUDA_R_16BF;
+    if (dtype != DType::F32 && dtype != DType::BF16) throw KernelError("linear_batched: float32 or bfloat16");
+    const float one = 1.f, zero = 0.f;
+    b.bind(s, "linear_batched");
+    // row-major W_b [N, K] is column-major [K, N] with leading dimension K, to be transposed; row-major [K, N] is column-major [N, K] as it stands
+    const cublasStatus_t st = cublasGemmStridedBatchedEx(b.handle, w_is_k_by_n ? CUBLAS_OP_N : CUBLAS_OP_T, CUBLAS_OP_N, N, T, K, &one, W, ty,
+                                                         w_is_k_by_n ? N : K, stride_w, x, ty, static_cast<int>(ldx), stride_x, &zero, out, ty,
+                                                         static_cast<int>(ldo), stride_o, batch, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    ++counters().library_calls;
+    if (st != CUBLAS_STATUS_SUCCESS) throw KernelError(format("linear_batched: the matrix-product library reported status %d", static_cast<int>(st)));
+    if (switches().sync) cuda_check(cudaStreamSynchronize(s), "linear_batched");
+}
+
 // ------------------------------------------------------------------------------------------------ attention
 namespace {
 constexpr int DECODE_COUNTERS = 1 << 16;

@@ -74,6 +74,11 @@ inline void swiglu(const void* gate_up, void* out, int T, int I, DType act, cuda
     check(vm_swiglu(gate_up, out, T, I, code(act), s), "swiglu", s);
 }
 
+inline void gated_activation(const void* gate_up, void* out, int T, int I, int kind, DType act, cudaStream_t s) {
+    Timed t("gated_activation", s);
+    check(vm_gated_activation(gate_up, out, T, I, kind, code(act), s), "gated_activation", s);
+}
+
 inline void convert(const void* in, DType in_dtype, void* out, DType out_dtype, long long n, cudaStream_t s) {
     Timed t("convert", s);
     check(vm_convert(in, code(in_dtype), out, code(out_dtype), n, s), "convert", s);
@@ -87,12 +92,51 @@ inline void rope_kv_write(void* qkv, const StepContext& ctx, const KVView& kv, c
           "rope_kv_write", ctx.stream);
 }
 
+inline void latent_norm_write(const float* down, int ld, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps, void* cq,
+                              const StepContext& ctx, const KVView& kv, bool write) {
+    Timed t("latent_norm_write", ctx.stream);
+    check(vm_latent_norm_write(down, ld, q_rank, kv_rank, wq, wkv, eps, cq, ctx.positions, ctx.seq_of_token, kv.block_table, kv.table_width,
+                               write ? kv.k_pages : nullptr, write ? kv.n_pages : 0, ctx.T, code(ctx.act_dtype), ctx.err, ctx.stream),
+          "latent_norm_write", ctx.stream);
+}
+
+inline void mlstm_scan(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, const StepContext& ctx, void* out, int H,
+                       int D, int V, float cap, float eps) {
+    Timed t("mlstm_scan", ctx.stream);
+    if (!ctx.state() || ctx.state_floats() != H * (D * V + D + 1)) throw CacheError("mlstm: the cache holds no state area of this layer's size");
+    check(vm_mlstm_scan(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, ctx.B, H, D, V, cap, eps, code(ctx.act_dtype),
+                        ctx.stream),
+          "mlstm_scan", ctx.stream);
+}
+
+inline void expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top, int* chosen,
+                          float* weight, float* shared_gate, DType act, cudaStream_t s) {
+    Timed t("expert_router", s);
+    check(vm_expert_router(x, w_router, b_router, w_gate, T, hidden, E, top, chosen, weight, shared_gate, code(act), s), "expert_router", s);
+}
+
+inline void experts_few_tokens(const void* x, const DeviceTensor& up, const DeviceTensor& down, const void* up_shared, const void* down_shared,
+                               const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff, int ff_shared, int top,
+                               int act_kind, int act_kind_shared, void* act, void* out, DType act_dtype, cudaStream_t s) {
+    Timed t("experts_few_tokens", s);
+    check(vm_experts_few_tokens(x, up.ptr, down.ptr, up_shared, down_shared, code(up.dtype), chosen, weight, shared_gate, T, hidden, ff, ff_shared, top,
+                                act_kind, act_kind_shared, act, out, code(act_dtype), s),
+          "experts_few_tokens", s);
+    ++counters().own_launches;          // two kernels
+}
+
 // out = x W^T.  x [T, K] (row stride ldx), W [N, K], out [T, N]; a library matrix product, as in the reference
 // (src/cuda/ops/matmul.cu:87-126); float32 runs without any reduced-precision mode.
 void linear(const void* x, DType x_dtype, long long ldx, const DeviceTensor& W, void* out, DType out_dtype, int T, cudaStream_t s);
 // h[T, N] += x W^T with the float32 residual stream h as the product's own accumulator (x and W bfloat16): the sum happens in
 // the library's float32 epilogue, and the kernel after it reads h alone.
 void linear_residual(const void* x, long long ldx, const DeviceTensor& W, float* h, int T, cudaStream_t s);
+
+// `batch` products with one stride per operand (the heads of an activation against the heads of a weight):
+// out_b[T, N] = x_b[T, K] W_b^T with W_b [N, K] row-major (transposed = false), or x_b W_b with W_b [K, N] row-major (true).
+// x, W and out have the same dtype (float32 or bfloat16); sums are float32.
+void linear_batched(const void* x, long long ldx, long long stride_x, const void* W, long long stride_w, bool w_is_k_by_n, void* out, long long ldo,
+                    long long stride_o, DType dtype, int T, int N, int K, int batch, cudaStream_t s);
 
 // attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype
 void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int D, float scale, int window);

@@ -124,7 +124,9 @@ Engine::Engine(std::shared_ptr<DecoderModel> m, const EngineOptions& o) : model(
     ops::cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "creating the engine's stream");
     // pages are whole: round the budget up
     const long long max_tokens = (std::max<long long>(o.max_tokens, 1) + VM_PAGE_TOKENS - 1) / VM_PAGE_TOKENS * VM_PAGE_TOKENS;
-    cache = std::make_unique<SequenceCache>(model->cache_needs(), model->cache_shares(), max_tokens, model->plan.max_positions, dtype, stream, o.max_slots);
+    // a plan without a limit of positions (0) is bounded by the cache alone
+    const int max_positions = model->plan.max_positions > 0 ? model->plan.max_positions : static_cast<int>(std::min<long long>(max_tokens, 1 << 30));
+    cache = std::make_unique<SequenceCache>(model->cache_needs(), model->cache_shares(), max_tokens, max_positions, dtype, stream, o.max_slots);
     impl_->err = std::make_unique<DeviceBuffer>(sizeof(int), true);
     // (waiting for the device after every launch, a debugging switch of the launch wrappers, cannot be recorded)
     use_graphs = (o.use_graphs != 0) && model->graph_safe() && !ops::sync_every_op();

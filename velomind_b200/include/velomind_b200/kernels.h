@@ -22,6 +22,8 @@ enum { VM_ERR_UNSUPPORTED = -1, VM_ERR_BAD_ARG = -2 };
 #define VM_PAGE_TOKENS 64
 // which two values of a head a rotary position encoding turns together: (j, j + rot_dim/2) or (2j, 2j + 1)
 enum { VM_PAIR_HALF_SPLIT = 0, VM_PAIR_INTERLEAVED = 1 };
+// activations of the feed-forward kernels: x sigmoid(x); the tanh form of GELU; max(x, 0)^2
+enum { VM_ACT_SILU = 0, VM_ACT_GELU_TANH = 1, VM_ACT_RELU_SQUARED = 2 };
 // error words a kernel may leave in `err`
 enum { VM_ERRWORD_TOKEN_ID = 1, VM_ERRWORD_CACHE_WRITE = 2, VM_ERRWORD_CACHE_READ = 3, VM_ERRWORD_BARRIER_WAIT = 4 };
 
@@ -34,6 +36,30 @@ int vm_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const
 int vm_residual_add(float* h, const void* delta, long long n, int act_dtype, cudaStream_t stream);
 int vm_swiglu(const void* gate_up, void* out, int T, int I, int act_dtype, cudaStream_t stream);
 int vm_convert(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i] for the activation `kind` (VM_ACT_*)
+int vm_gated_activation(const void* gate_up, void* out, int T, int I, int kind, int act_dtype, cudaStream_t stream);
+
+// ---- latent_cache.cu: the norms of a latent-attention layer's two down projections and the cache write of the key/value latent
+// down float32 [T, ld]: columns [0, q_rank) and, if `pages` is given, [q_rank, q_rank + kv_rank); cq [T, q_rank] and the
+// pages [n_pages, VM_PAGE_TOKENS, kv_rank] in the activation dtype
+int vm_latent_norm_write(const float* down, int ld, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps, void* cq,
+                         const int* positions, const int* seq_of_token, const int* block_table, int max_blocks, void* pages,
+                         int n_pages, int T, int act_dtype, int* err, cudaStream_t stream);
+
+// ---- mlstm.cu: the matrix-memory recurrence with its output stage
+// proj float32 [T, ld]: q | k | v | g | x_i | x_f (H*D, H*D, H*V, H*V, H, H columns); state float32, per slot and head S [D, V], n [D], m;
+// out [T, H*V] in the activation dtype
+int vm_mlstm_scan(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state,
+                  const int* cu_tokens, const int* slots, void* out, int B, int H, int D, int V, float cap, float eps, int act_dtype,
+                  cudaStream_t stream);
+
+// ---- routed_experts.cu: a routed feed-forward for few tokens
+int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
+                     int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream);
+int vm_experts_few_tokens(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared,
+                          int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
+                          int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, int act_dtype,
+                          cudaStream_t stream);
 
 // ---- rope_cache.cu
 int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,

@@ -179,7 +179,7 @@ struct ModelPlan {
     std::string final_norm_prefix;
     PartSpec head;
     std::string head_prefix;
-    int max_positions = 0;
+    int max_positions = 0;                    // 0: the architecture sets no limit (the cache's size is the only one)
     std::vector<int> stop_tokens;
     std::optional<int> bos_token;
     json::Value describe;                     // what a console's /model shows (sizes by name), filled by the architecture
@@ -308,7 +308,7 @@ private:
 struct CacheNeed {
     enum Kind { None, All, Window } kind = None;   // every earlier key/value; the last `window`; nothing
     int kv_heads = 0;
-    int key_dim = 0, value_dim = 0;                // per head; the paged storage of this library wants them equal
+    int key_dim = 0, value_dim = 0;                // per head; the paged storage wants them equal, or value_dim 0: one row per token only
     int window = 0;
     int state_floats = 0;                          // fixed-size float32 state per sequence (0: none)
     bool same_group(const CacheNeed& o) const {
@@ -435,7 +435,7 @@ struct RotaryTable {                            // what a position encoding hand
 
 struct KVView {
     void* k_pages = nullptr;                    // [n_pages, kv_heads, VM_PAGE_TOKENS, head_dim]
-    void* v_pages = nullptr;
+    void* v_pages = nullptr;                    // null for a group that keeps one row per token
     const int* block_table = nullptr;           // device int32 [B, table_width]
     int table_width = 0, n_pages = 0;
     bool owns = true;                           // false: the run reads another run's cache and must not write it

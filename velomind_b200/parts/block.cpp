@@ -11,7 +11,7 @@ namespace vmb {
 // into its first kernel and the residual sum into its last one (can_fuse / forward_fused) does so.
 class PreNormBlock : public Arrangement {
 public:
-    explicit PreNormBlock(const BlockParts& p) : p_(p) {}
+    explicit PreNormBlock(const BlockParts& p, bool feed_forward = true) : p_(p), feed_forward_(feed_forward) {}
     bool graph_safe() const override { return true; }
 
     void* forward(StepContext& ctx, float* h, void* pending) override {
@@ -28,6 +28,7 @@ public:
             p_.mixer->forward(ctx, x, pending);
             ctx.give(x);
         }
+        if (!feed_forward_) return pending;        // a layer that is its mixer alone
         if (p_.feed_forward->can_fuse(ctx, *p_.feed_forward_norm)) {
             settle(ctx, h, pending, hid);
             p_.feed_forward->forward_fused(ctx, h, *p_.feed_forward_norm);
@@ -51,12 +52,23 @@ private:
         ctx.give(pending);
     }
     BlockParts p_;
+    bool feed_forward_;
+};
+
+// The feed-forward of a layer that has none: no weights, never run.
+class NoFeedForward : public FeedForward {
+public:
+    bool graph_safe() const override { return true; }
+    void forward(StepContext&, const void*, void*) override { throw Error("a feed-forward of kind 'none' stands for a part that is not there; it cannot run"); }
 };
 
 namespace {
 struct Reg {
     Reg() {
         register_arrangement("prenorm", [](const json::Value&, const BlockParts& parts) { return std::make_shared<PreNormBlock>(parts); });
+        // h += mixer(norm(h)) and nothing else: the layer's feed-forward and its norm are parts of kind "none"
+        register_arrangement("prenorm_mixer", [](const json::Value&, const BlockParts& parts) { return std::make_shared<PreNormBlock>(parts, false); });
+        register_part("feed_forward", "none", [](const json::Value&) { return std::make_shared<NoFeedForward>(); });
     }
 } reg;
 }  // namespace

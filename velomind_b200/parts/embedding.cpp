@@ -7,18 +7,20 @@ namespace vmb {
 // h[t, :] = table[token[t], :] into the float32 residual stream (src/cpu/ops/embedding.cpp:27-32).
 class TokenEmbedding : public Embedding {
 public:
-    TokenEmbedding(int vocab, int hidden) : vocab_(vocab), hidden_(hidden) {}
+    // `tensor`: what the table is called behind the part's prefix ("weight" unless the checkpoint says otherwise; may be empty)
+    TokenEmbedding(int vocab, int hidden, std::string tensor = "weight") : vocab_(vocab), hidden_(hidden), tensor_(std::move(tensor)) {}
     WeightTable weight_specs() const override {
         WeightTable t;
-        t["weight"].shape = {vocab_, hidden_};
+        t[tensor_].shape = {vocab_, hidden_};
         return t;
     }
-    void bind(const Weights& w, BindContext& bc) override { table_ = bc.upload(w.at("weight"), bc.matrix_dtype({&w.at("weight")})); }
+    void bind(const Weights& w, BindContext& bc) override { table_ = bc.upload(w.at(tensor_), bc.matrix_dtype({&w.at(tensor_)})); }
     bool graph_safe() const override { return true; }
     void forward(StepContext& ctx, const int* tokens, float* h) override { ops::embed_gather(table_, tokens, h, ctx.T, hidden_, ctx.err, ctx.stream); }
 
 private:
     int vocab_, hidden_;
+    std::string tensor_;
     DeviceTensor table_;
 };
 
@@ -27,14 +29,15 @@ private:
 // then shared with the embedding, not copied.
 class LinearHead : public Head {
 public:
-    LinearHead(int vocab, int hidden, std::string tied_to) : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)) {}
+    LinearHead(int vocab, int hidden, std::string tied_to, std::string tensor = "weight")
+        : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)), tensor_(std::move(tensor)) {}
     WeightTable weight_specs() const override {
         WeightTable t;
-        t["weight"].shape = {vocab_, hidden_};
-        t["weight"].alias_of = tied_to_;
+        t[tensor_].shape = {vocab_, hidden_};
+        t[tensor_].alias_of = tied_to_;
         return t;
     }
-    void bind(const Weights& w, BindContext& bc) override { proj_.bind({&w.at("weight")}, bc); }
+    void bind(const Weights& w, BindContext& bc) override { proj_.bind({&w.at(tensor_)}, bc); }
     bool graph_safe() const override { return true; }
     void forward(StepContext& ctx, const void* x, float* logits) override {
         if (ctx.act_dtype == DType::BF16 && ops::skinny_ok(ctx.R, hidden_, proj_.weight) && vocab_ % 8 == 0 && ctx.R_cap <= ops::SKINNY_HEAD_MAX_ROWS)
@@ -45,17 +48,18 @@ public:
 
 private:
     int vocab_, hidden_;
-    std::string tied_to_;
+    std::string tied_to_, tensor_;
     Linear proj_;
 };
 
 namespace {
 RegisterPart reg_embed("embedding", "token_table", [](const json::Value& a) {
-    return std::make_shared<TokenEmbedding>(static_cast<int>(arg_int(a, "vocab", "token_table")), static_cast<int>(arg_int(a, "hidden", "token_table")));
+    return std::make_shared<TokenEmbedding>(static_cast<int>(arg_int(a, "vocab", "token_table")), static_cast<int>(arg_int(a, "hidden", "token_table")),
+                                            arg_string_or(a, "tensor", "weight", "token_table"));
 });
 RegisterPart reg_head("head", "linear", [](const json::Value& a) {
     return std::make_shared<LinearHead>(static_cast<int>(arg_int(a, "vocab", "linear")), static_cast<int>(arg_int(a, "hidden", "linear")),
-                                        arg_string_or(a, "tied_to", "", "linear"));
+                                        arg_string_or(a, "tied_to", "", "linear"), arg_string_or(a, "tensor", "weight", "linear"));
 });
 }  // namespace
 

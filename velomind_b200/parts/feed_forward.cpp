@@ -1,4 +1,4 @@
-// Gated feed-forward (SwiGLU).
+// Gated feed-forward: down(act(gate(x)) * up(x)); SwiGLU with act = SiLU.
 #include "args.h"
 #include "linear.h"
 
@@ -6,21 +6,26 @@ namespace vmb {
 
 // down(silu(gate(x)) * up(x)), no biases (examples/common/llama/llama_graph.cpp:22-28,122-138).  gate and up are one
 // stacked product; the activation kernel reads both halves.
+//
+// `activation` (VM_ACT_*) and the three tensors' names are arguments; the fused kernels know SiLU, any other activation runs
+// as product, activation kernel, product.
 class SwiGLU : public FeedForward {
 public:
-    SwiGLU(int hidden, int intermediate) : hidden_(hidden), I_(intermediate) {}
+    SwiGLU(int hidden, int intermediate, int activation = VM_ACT_SILU, std::string gate = "gate_proj.weight", std::string up = "up_proj.weight",
+           std::string down = "down_proj.weight")
+        : hidden_(hidden), I_(intermediate), act_(activation), gate_name_(std::move(gate)), up_name_(std::move(up)), down_name_(std::move(down)) {}
 
     WeightTable weight_specs() const override {
         WeightTable t;
-        t["gate_proj.weight"].shape = {I_, hidden_};
-        t["up_proj.weight"].shape = {I_, hidden_};
-        t["down_proj.weight"].shape = {hidden_, I_};
+        t[gate_name_].shape = {I_, hidden_};
+        t[up_name_].shape = {I_, hidden_};
+        t[down_name_].shape = {hidden_, I_};
         return t;
     }
 
     void bind(const Weights& w, BindContext& bc) override {
-        gate_up_.bind({&w.at("gate_proj.weight"), &w.at("up_proj.weight")}, bc);
-        down_.bind({&w.at("down_proj.weight")}, bc);
+        gate_up_.bind({&w.at(gate_name_), &w.at(up_name_)}, bc);
+        down_.bind({&w.at(down_name_)}, bc);
     }
 
     bool graph_safe() const override { return true; }
@@ -33,6 +38,7 @@ public:
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
+        if (act_ != VM_ACT_SILU) return false;
         if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
         if (gate_up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
         if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && I_ % 32 == 0;
@@ -79,20 +85,30 @@ public:
         void* gu = ctx.take_tokens(2ll * I_, ctx.act_dtype);
         gate_up_.apply(ctx, x, ctx.act_dtype, gu, ctx.act_dtype, ctx.T, ctx.T_cap);
         void* act = ctx.take_tokens(I_, ctx.act_dtype);
-        ops::swiglu(gu, act, ctx.T, I_, ctx.act_dtype, ctx.stream);
+        ops::gated_activation(gu, act, ctx.T, I_, act_, ctx.act_dtype, ctx.stream);
         ctx.give(gu);
         down_.apply(ctx, act, ctx.act_dtype, out, ctx.act_dtype, ctx.T, ctx.T_cap);
         ctx.give(act);
     }
 
 private:
-    int hidden_, I_;
+    int hidden_, I_, act_;
+    std::string gate_name_, up_name_, down_name_;
     Linear gate_up_, down_;
 };
+
+int activation_code(const std::string& name, const char* part);     // parts/routed_experts.cpp
 
 namespace {
 RegisterPart reg("feed_forward", "swiglu", [](const json::Value& a) {
     return std::make_shared<SwiGLU>(static_cast<int>(arg_int(a, "hidden", "swiglu")), static_cast<int>(arg_int(a, "intermediate", "swiglu")));
+});
+// the same unit with the activation and the tensor names as arguments
+RegisterPart reg_gated("feed_forward", "gated", [](const json::Value& a) {
+    const char* k = "gated";
+    return std::make_shared<SwiGLU>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "intermediate", k)),
+                                    activation_code(arg_string_or(a, "activation", "silu", k), k), arg_string_or(a, "gate", "gate_proj.weight", k),
+                                    arg_string_or(a, "up", "up_proj.weight", k), arg_string_or(a, "down", "down_proj.weight", k));
 });
 }  // namespace
 

@@ -1,0 +1,103 @@
+// A routed feed-forward (mixture of experts) with an optional shared expert.
+//
+//   z = W_router x + b (float32)          the `top` experts with the largest logits are chosen
+//   w = softmax over the chosen logits    y = sum_k w_k W_down[e_k] act(W_up[e_k] x)
+//   shared expert (if any): runs for every token and is added, times sigmoid(w_sg . x) if it has a gate
+//
+// Experts are two-layer networks without biases; `activation` names theirs (the shared expert may have another).  The router,
+// its bias and the shared gate stay float32 on the device whatever the compute dtype.
+#include "args.h"
+#include "linear.h"
+
+namespace vmb {
+
+int activation_code(const std::string& name, const char* part) {
+    if (name == "silu") return VM_ACT_SILU;
+    if (name == "gelu_tanh") return VM_ACT_GELU_TANH;
+    if (name == "relu_squared") return VM_ACT_RELU_SQUARED;
+    throw ConfigError(format("part '%s': activation '%s' is not known (silu, gelu_tanh, relu_squared)", part, name.c_str()));
+}
+
+class RoutedExperts : public FeedForward {
+public:
+    RoutedExperts(int hidden, int experts, int top, int ff, int act, int shared_ff, int shared_act, bool shared_gate)
+        : hidden_(hidden), E_(experts), top_(top), ff_(ff), act_(act), sff_(shared_ff), sact_(shared_act), gate_(shared_gate && shared_ff > 0) {
+        if (top < 1 || top > experts) throw ConfigError(format("part 'routed_experts': top (%d) must be within 1..experts (%d)", top, experts));
+    }
+
+    WeightTable weight_specs() const override {
+        WeightTable t;
+        t["router"].shape = {E_, hidden_};
+        t["router.b"].shape = {E_};
+        for (int e = 0; e < E_; ++e) {
+            t[format("e%d.up", e)].shape = {ff_, hidden_};
+            t[format("e%d.down", e)].shape = {hidden_, ff_};
+        }
+        if (sff_ > 0) {
+            t["shared.up"].shape = {sff_, hidden_};
+            t["shared.down"].shape = {hidden_, sff_};
+            if (gate_) t["shared.sg"].shape = {1, hidden_};
+        }
+        return t;
+    }
+
+    void bind(const Weights& w, BindContext& bc) override {
+        router_ = bc.upload(w.at("router"), DType::F32);
+        router_b_ = bc.upload(w.at("router.b"), DType::F32);
+        std::vector<const HostTensor*> ups, downs, all;
+        for (int e = 0; e < E_; ++e) {
+            ups.push_back(&w.at(format("e%d.up", e)));
+            downs.push_back(&w.at(format("e%d.down", e)));
+        }
+        all = ups;
+        all.insert(all.end(), downs.begin(), downs.end());
+        if (sff_ > 0) {
+            all.push_back(&w.at("shared.up"));
+            all.push_back(&w.at("shared.down"));
+        }
+        const DType kept = bc.matrix_dtype(all);           // one dtype for every expert matrix
+        up_ = bc.upload_stacked(ups, kept);
+        down_ = bc.upload_stacked(downs, kept);
+        if (sff_ > 0) {
+            s_up_ = bc.upload(w.at("shared.up"), kept);
+            s_down_ = bc.upload(w.at("shared.down"), kept);
+            if (gate_) s_gate_ = bc.upload(w.at("shared.sg"), DType::F32);
+        }
+    }
+
+    bool graph_safe() const override { return true; }
+
+    void forward(StepContext& ctx, const void* x, void* out) override {
+        int* chosen = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
+        float* weight = static_cast<float*>(ctx.take_tokens(top_, DType::F32));
+        float* sgate = gate_ ? static_cast<float*>(ctx.take_tokens(1, DType::F32)) : nullptr;
+        ops::expert_router(x, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
+                           gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
+                           ctx.stream);
+        void* act = ctx.take_tokens(static_cast<long long>(top_) * ff_ + sff_, ctx.act_dtype);
+        ops::experts_few_tokens(x, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T, hidden_,
+                                ff_, sff_, top_, act_, sact_, act, out, ctx.act_dtype, ctx.stream);
+        ctx.give(act);
+        ctx.give(sgate);
+        ctx.give(weight);
+        ctx.give(chosen);
+    }
+
+private:
+    int hidden_, E_, top_, ff_, act_, sff_, sact_;
+    bool gate_;
+    DeviceTensor router_, router_b_, up_, down_, s_up_, s_down_, s_gate_;
+};
+
+namespace {
+RegisterPart reg("feed_forward", "routed_experts", [](const json::Value& a) {
+    const char* k = "routed_experts";
+    const std::string act = arg_string_or(a, "activation", "relu_squared", k);
+    return std::make_shared<RoutedExperts>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "experts", k)),
+                                           static_cast<int>(arg_int(a, "top", k)), static_cast<int>(arg_int(a, "ff", k)), activation_code(act, k),
+                                           static_cast<int>(arg_int_or(a, "shared_ff", 0, k)),
+                                           activation_code(arg_string_or(a, "shared_activation", act, k), k), arg_int_or(a, "shared_gate", 1, k) != 0);
+});
+}  // namespace
+
+}  // namespace vmb
