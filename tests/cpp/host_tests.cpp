@@ -142,6 +142,22 @@ TEST(groups_with_different_needs_have_their_own_storage) {
     CacheNeed unequal = all_keys(2, 16);
     unequal.value_dim = 32;
     THROWS(CacheError, "keys of 16 and values of 32", CacheBook({unequal}, {-1}, 64 * 4, 256));
+    // one row per token and no second one (a latent that is key and value at once) is a group like any other; a run that keeps
+    // only a fixed-size state has none; a run may read another run's rows
+    CacheNeed latent = all_keys(1, 48);
+    latent.value_dim = 0;
+    CacheNeed memory_only;
+    memory_only.state_floats = 100;
+    CacheBook mixed({latent, memory_only, CacheNeed{}, all_keys(1, 48)}, {-1, -1, 0, -1}, 64 * 4, 256);
+    CHECK(mixed.groups.size() == 2 && mixed.where(0) == mixed.where(2) && mixed.where(1).first == -1 && mixed.where(3).first == 1);
+    CHECK(mixed.state_floats[1] == 100 && mixed.state_owner[1] == 1 && mixed.state_owner[0] == -1);
+    CacheBook no_keys({memory_only}, {-1}, 64 * 4, 256);
+    const int only = no_keys.open();
+    no_keys.reserve(only, 200);
+    no_keys.commit(only, 200);
+    CHECK(no_keys.groups.empty() && no_keys.tokens_held() == 0 && no_keys.length[only] == 200);
+    no_keys.close(only);
+    no_keys.check();
 }
 
 // ------------------------------------------------------------------------------------------------ arena
@@ -414,7 +430,7 @@ TEST(json_reads_and_writes) {
 }
 
 TEST(parts_and_architectures_are_looked_up_by_name) {
-    THROWS(ConfigError, "no norm of kind 'layernorm' is registered; registered: rmsnorm", build_part("norm", PartSpec{"layernorm", json::Value()}));
+    THROWS(ConfigError, "no norm of kind 'layernorm' is registered; registered: none, rmsnorm", build_part("norm", PartSpec{"layernorm", json::Value()}));
     THROWS(ConfigError, "unknown role", register_part("gadget", "x", nullptr));
     const std::vector<std::string> positions = registered_parts("position");
     CHECK(std::find(positions.begin(), positions.end(), "rotary_interleaved") != positions.end());
