@@ -159,10 +159,14 @@ def test_whole_model_float32(which, kog_folders):
 
 def test_whole_model_bfloat16(kog_folders, tmp_path):
     """The serving precision: weights rounded to bfloat16, then compared with the plain implementation on the SAME rounded
-    weights.  A routed layer may choose another expert for a token whose two logits are closer than the rounding of its
-    input, so a few positions may be far off; all others must be close, and most very close."""
+    weights.  A routed layer would choose another expert for a token whose two logits are closer than the rounding of its
+    input, and the answer would then differ by more than rounding; so here every routed layer takes ALL its experts (their
+    weights are still the softmax of the router's logits), and the choice itself is left to the float32 tests."""
     import velomind_b200 as vm
     cfg, w = K.read_model(kog_folders["b"])
+    for layer in cfg["layers"]:
+        if layer["mlp"] and layer["mlp"]["kind"] == "moe":
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
     bits = rounded_to_bf16(w)
     folder = write_model(str(tmp_path / "b16"), cfg, bits, as_bf16=True)
     engine = vm.Engine(vm.load_model(folder, "bfloat16", "cuda:0"), 64 * 16, max_slots=4)
@@ -173,7 +177,8 @@ def test_whole_model_bfloat16(kog_folders, tmp_path):
         got = S.run_steps_in_process(engine, steps)
         exp = S.expected_rows(steps, requests, plain)
         err = np.concatenate([np.abs(got[k] - exp[k]).max(axis=1) for k in exp]) / scale
-        assert np.median(err) < 0.02 and np.mean(err < 0.05) > 0.95, (float(np.median(err)), float(np.mean(err < 0.05)))
+        # rounding alone: about one part in a hundred of the largest logit at most places, several times that at the worst of hundreds
+        assert np.median(err) < 0.02 and err.max() < 0.15, (float(np.median(err)), float(err.max()))
 
 
 def test_decode_steps_are_replayed_from_graphs(kog_folders):

@@ -123,7 +123,244 @@ int launch_scan(const float* proj, int ld, const float* bias_i, const float* bia
     return vm_launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------ chunk by chunk
+// Inside a chunk of L tokens that starts from (S', n', m') the recurrence has a closed form.  With F_j the sum of the log
+// forget gates up to token j of the chunk, a_s = i_s - F_s and g_j = max(m', max_{s<=j} a_s):
+//     m_j   = F_j + g_j
+//     S_j   = exp(m' - g_j) S' + sum_{s<=j} exp(a_s - g_j) k_s v_s^T          (every exponent is <= 0)
+//     S_j^T q_j = exp(m' - g_j) S'^T q_j + sum_{s<=j} exp(a_s - g_j) (k_s . q_j) v_s
+//     n_j . q_j = exp(m' - g_j) n' . q_j + sum_{s<=j} exp(a_s - g_j) (k_s . q_j)
+// so a chunk is three small matrix products (q k^T, weights times v, q times the old state) and the state moves on once per
+// chunk.  F, a and g are summed in float64 and differences are taken there, so that a long chunk of strong forget gates does
+// not cost the weights their float32 digits; everything else is float32.
+//
+// One block per (slice of value columns, head, sequence): the slice's columns of S live in shared memory for the whole
+// prompt.  Every slice needs the scores and n . q, and computes them itself.  The un-normalised o goes to a float32 buffer
+// (the unit norm needs all slices of a head), n and m of the sequence's end to a scratch row; the output kernel that follows
+// finishes both.
+constexpr int CHUNK_THREADS = 256;
+
+struct ChunkSizes {
+    int L, VS, slices;
+    size_t smem;
+};
+
+__host__ __device__ inline size_t chunk_smem_floats(int L, int D, int VS) {
+    // Q [L, D+1], Kt [D, L], Vs [L, VS], P [L, L], S [D, VS], n [D], nq [L], wdec [L], wend [L], doubles a [L], g [L] (as 4 L floats)
+    return (size_t)L * (D + 1) + (size_t)D * L + (size_t)L * VS + (size_t)L * L + (size_t)D * VS + D + 3 * (size_t)L + 4 * (size_t)L;
+}
+
+__global__ void __launch_bounds__(CHUNK_THREADS)
+mlstm_chunk_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
+                   float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ slots, float* __restrict__ o_raw,
+                   float* __restrict__ end_nm, int H, int D, int V, int L, int VS, float cap) {
+    extern __shared__ __align__(16) float sm[];
+    float* Q = sm;                                   // [L, D + 1]
+    float* Kt = Q + (size_t)L * (D + 1);             // [D, L]
+    float* Vs = Kt + (size_t)D * L;                  // [L, VS]
+    float* P = Vs + (size_t)L * VS;                  // [L, L]
+    float* S = P + (size_t)L * L;                    // [D, VS]
+    float* nv = S + (size_t)D * VS;                  // [D]
+    float* nq = nv + D;                              // [L]
+    float* wdec = nq + L;                            // [L] exp(m' - g_j)
+    float* wend = wdec + L;                          // [L] exp(a_s - g_last)
+    double* a_s = reinterpret_cast<double*>(wend + L + ((reinterpret_cast<uintptr_t>(wend + L) & 7) ? 1 : 0));   // [L]
+    double* g_s = a_s + L;                           // [L]
+    __shared__ double m_carry;
+    const int slice = blockIdx.x, h = blockIdx.y, s = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
+    if (t1 <= t0) return;
+    const int v0 = slice * VS, vs = min(VS, V - v0);
+    const size_t head_floats = (size_t)D * V + D + 1;
+    float* st = state + ((size_t)slots[s] * H + h) * head_floats;
+    for (int i = tid; i < D * vs; i += CHUNK_THREADS) { const int d = i / vs, v = i - d * vs; S[d * VS + v] = st[(size_t)d * V + v0 + v]; }
+    for (int d = tid; d < D; d += CHUNK_THREADS) nv[d] = st[(size_t)D * V + d];
+    if (tid == 0) m_carry = (double)st[(size_t)D * V + D];
+    const int off_k = H * D, off_v = 2 * H * D, off_i = 2 * H * D + 2 * H * V, off_f = off_i + H;
+    const float q_scale = rsqrtf((float)D);
+    const float bi = bias_i[h], bf = bias_f[h];
+    __syncthreads();
+    for (int c0 = t0; c0 < t1; c0 += L) {
+        const int Lc = min(L, t1 - c0);
+        // ---- the chunk's q, k, v
+        for (int i = tid; i < Lc * D; i += CHUNK_THREADS) {
+            const int j = i / D, d = i - j * D;
+            const float* row = proj + (size_t)(c0 + j) * ld;
+            Q[j * (D + 1) + d] = row[h * D + d] * q_scale;
+            Kt[d * L + j] = row[off_k + h * D + d];
+        }
+        for (int i = tid; i < Lc * vs; i += CHUNK_THREADS) {
+            const int j = i / vs, v = i - j * vs;
+            Vs[j * VS + v] = proj[(size_t)(c0 + j) * ld + off_v + h * V + v0 + v];
+        }
+        // ---- gates: F (inclusive sums of the log forget gates), a = i - F, g = max(m', running max of a); one warp, float64
+        if (warp == 0) {
+            const double m_prev = m_carry;
+            double run_f = 0.0, run_a = -1e300;
+            for (int base = 0; base < Lc; base += 32) {
+                const int j = base + lane;
+                double fg = 0.0, ig = 0.0;
+                if (j < Lc) {
+                    const float* row = proj + (size_t)(c0 + j) * ld;
+                    ig = (double)soft_cap(row[off_i + h] + bi, cap);
+                    fg = (double)log_sigmoid(soft_cap(row[off_f + h] + bf, cap));
+                }
+                double F = fg;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const double up = __shfl_up_sync(0xffffffffu, F, o); if (lane >= o) F += up; }
+                F += run_f;
+                double a = j < Lc ? ig - F : -1e300;
+                double mx = a;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const double up = __shfl_up_sync(0xffffffffu, mx, o); if (lane >= o) mx = fmax(mx, up); }
+                mx = fmax(mx, run_a);
+                if (j < Lc) {
+                    a_s[j] = a;
+                    g_s[j] = fmax(m_prev, mx);
+                    wdec[j] = expf((float)(m_prev - fmax(m_prev, mx)));
+                }
+                run_f = __shfl_sync(0xffffffffu, F, 31);
+                run_a = __shfl_sync(0xffffffffu, mx, 31);
+                if (base + 32 >= Lc && lane == ((Lc - 1) & 31)) m_carry = F + fmax(m_prev, mx);     // m after the chunk's last token
+            }
+        }
+        __syncthreads();
+        // ---- weighted scores P[j][s] = exp(a_s - g_j) (q_j . k_s), s <= j; and the weights of the chunk's tokens in the new state
+        for (int i = tid; i < Lc * Lc; i += CHUNK_THREADS) {
+            const int j = i / Lc, ss = i - j * Lc;
+            float p = 0.f;
+            if (ss <= j) {
+                const float* qj = Q + j * (D + 1);
+                float acc = 0.f;
+                for (int d = 0; d < D; ++d) acc = fmaf(qj[d], Kt[d * L + ss], acc);
+                p = acc * expf((float)(a_s[ss] - g_s[j]));
+            }
+            P[j * L + ss] = p;
+        }
+        for (int j = tid; j < Lc; j += CHUNK_THREADS) wend[j] = expf((float)(a_s[j] - g_s[Lc - 1]));
+        __syncthreads();
+        // ---- n_j . q_j, a warp per row
+        for (int j = warp; j < Lc; j += CHUNK_THREADS / 32) {
+            float acc = 0.f;
+            for (int ss = lane; ss <= j; ss += 32) acc += P[j * L + ss];
+            float old = 0.f;
+            for (int d = lane; d < D; d += 32) old = fmaf(nv[d], Q[j * (D + 1) + d], old);
+            acc = vm_warp_sum(fmaf(wdec[j], old, acc));
+            if (lane == 0) nq[j] = acc;
+        }
+        __syncthreads();
+        // ---- o_j[v] = (exp(m' - g_j) S'^T q_j + sum_s P[j][s] v_s) / (max(|n_j . q_j|, exp(-m_j)) + 1e-6)
+        for (int i = tid; i < Lc * vs; i += CHUNK_THREADS) {
+            const int j = i / vs, v = i - j * vs;
+            const float* qj = Q + j * (D + 1);
+            float old = 0.f;
+            for (int d = 0; d < D; ++d) old = fmaf(qj[d], S[d * VS + v], old);
+            float acc = 0.f;
+            for (int ss = 0; ss <= j; ++ss) acc = fmaf(P[j * L + ss], Vs[ss * VS + v], acc);
+            const float num = fmaf(wdec[j], old, acc);
+            // m_j = F_j + g_j and F_j = i_j - a_j are not kept; exp(-m_j) from the float64 pieces
+            const float* row = proj + (size_t)(c0 + j) * ld;
+            const double m_j = ((double)soft_cap(row[off_i + h] + bi, cap) - a_s[j]) + g_s[j];
+            const float den = fmaxf(fabsf(nq[j]), expf((float)(-m_j))) + 1e-6f;
+            o_raw[(size_t)(c0 + j) * H * V + h * V + v0 + v] = num / den;
+        }
+        __syncthreads();
+        // ---- the state after the chunk
+        const float keep = wdec[Lc - 1];
+        for (int i = tid; i < D * vs; i += CHUNK_THREADS) {
+            const int d = i / vs, v = i - d * vs;
+            float acc = keep * S[d * VS + v];
+            const float* kd = Kt + d * L;
+            for (int ss = 0; ss < Lc; ++ss) acc = fmaf(wend[ss] * kd[ss], Vs[ss * VS + v], acc);
+            S[d * VS + v] = acc;
+        }
+        for (int d = tid; d < D; d += CHUNK_THREADS) {
+            float acc = keep * nv[d];
+            const float* kd = Kt + d * L;
+            for (int ss = 0; ss < Lc; ++ss) acc = fmaf(wend[ss], kd[ss], acc);
+            nv[d] = acc;
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < D * vs; i += CHUNK_THREADS) { const int d = i / vs, v = i - d * vs; st[(size_t)d * V + v0 + v] = S[d * VS + v]; }
+    if (slice == 0) {
+        float* e = end_nm + ((size_t)s * H + h) * (D + 1);
+        for (int d = tid; d < D; d += CHUNK_THREADS) e[d] = nv[d];
+        if (tid == 0) e[D] = (float)m_carry;
+    }
+}
+
+// The output stage after the chunk kernel: a warp per (token, head) divides o by its root mean square, applies the learned
+// scale and the sigmoid gate; the first warps also move the sequences' new n and m from the scratch rows into the state.
+template <typename T>
+__global__ void mlstm_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, const float* __restrict__ norm_w,
+                                    T* __restrict__ out, int n_tokens, int H, int D, int V, float eps, const float* __restrict__ end_nm,
+                                    float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ slots, int B) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w < (long long)B * H) {
+        const int s = (int)(w / H), h = (int)(w % H);
+        if (cu_tokens[s + 1] > cu_tokens[s]) {
+            const float* e = end_nm + ((size_t)s * H + h) * (D + 1);
+            float* st = state + ((size_t)slots[s] * H + h) * ((size_t)D * V + D + 1) + (size_t)D * V;
+            for (int d = lane; d <= D; d += 32) st[d] = e[d];
+        }
+    }
+    if (w >= (long long)n_tokens * H) return;
+    const int t = (int)(w / H), h = (int)(w % H);
+    const float* o = o_raw + (size_t)t * H * V + h * V;
+    float ss = 0.f;
+    for (int v = lane; v < V; v += 32) ss = fmaf(o[v], o[v], ss);
+    ss = vm_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    const float* gate = proj + (size_t)t * ld + 2 * H * D + H * V + h * V;
+    for (int v = lane; v < V; v += 32)
+        out[(size_t)t * H * V + h * V + v] = vm_from_float<T>(o[v] * inv * norm_w[h * V + v] * (1.0f / (1.0f + expf(-gate[v]))));
+}
+
+ChunkSizes chunk_sizes(int D, int V) {
+    ChunkSizes c;
+    c.VS = V <= 64 ? V : 64;
+    c.slices = (V + c.VS - 1) / c.VS;
+    c.L = 64;
+    while (c.L > 8 && chunk_smem_floats(c.L, D, c.VS) * sizeof(float) + 64 > 200 * 1024) c.L /= 2;
+    c.smem = chunk_smem_floats(c.L, D, c.VS) * sizeof(float) + 64;
+    return c;
+}
+
 }  // namespace
+
+// scratch floats the chunkwise form needs: the un-normalised o [T, H*V] and a row of n, m per (sequence, head)
+VM_API long long vm_mlstm_chunk_scratch_floats(int T, int B, int H, int D, int V) { return (long long)T * H * V + (long long)B * H * (D + 1); }
+
+VM_API int vm_mlstm_chunks(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state, const int* cu_tokens,
+                           const int* slots, void* out, float* scratch, int T, int B, int H, int D, int V, float cap, float eps, int act_dtype,
+                           cudaStream_t stream) {
+    if (B <= 0 || T <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || ld < 2 * H * D + 2 * H * V + 2 * H || !(cap > 0.f)) return VM_ERR_BAD_ARG;
+    const ChunkSizes c = chunk_sizes(D, V);
+    if (c.smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
+    static size_t raised = 0;
+    if (c.smem > 48 * 1024 && c.smem > raised) {
+        if (cudaFuncSetAttribute(mlstm_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return vm_launch_status();
+        raised = c.smem;
+    }
+    float* o_raw = scratch;
+    float* end_nm = scratch + (size_t)T * H * V;
+    mlstm_chunk_kernel<<<dim3(c.slices, H, B), CHUNK_THREADS, c.smem, stream>>>(proj, ld, bias_i, bias_f, state, cu_tokens, slots, o_raw, end_nm, H, D, V,
+                                                                                  c.L, c.VS, cap);
+    int st = vm_launch_status();
+    if (st) return st;
+    const long long warps = (long long)T * H > (long long)B * H ? (long long)T * H : (long long)B * H;
+    const int blocks = (int)((warps + 7) / 8);
+    if (act_dtype == VM_F32)
+        mlstm_output_kernel<float><<<blocks, 256, 0, stream>>>(o_raw, proj, ld, norm_w, (float*)out, T, H, D, V, eps, end_nm, state, cu_tokens, slots, B);
+    else if (act_dtype == VM_BF16)
+        mlstm_output_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(o_raw, proj, ld, norm_w, (__nv_bfloat16*)out, T, H, D, V, eps, end_nm, state,
+                                                                       cu_tokens, slots, B);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
 
 VM_API int vm_mlstm_scan(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state, const int* cu_tokens,
                          const int* slots, void* out, int B, int H, int D, int V, float cap, float eps, int act_dtype, cudaStream_t stream) {

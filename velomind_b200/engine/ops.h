@@ -100,13 +100,25 @@ inline void latent_norm_write(const float* down, int ld, int q_rank, int kv_rank
           "latent_norm_write", ctx.stream);
 }
 
+constexpr int MLSTM_SCAN_MAX_TOKENS = 8;
 inline void mlstm_scan(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, const StepContext& ctx, void* out, int H,
                        int D, int V, float cap, float eps) {
     Timed t("mlstm_scan", ctx.stream);
     if (!ctx.state() || ctx.state_floats() != H * (D * V + D + 1)) throw CacheError("mlstm: the cache holds no state area of this layer's size");
-    check(vm_mlstm_scan(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, ctx.B, H, D, V, cap, eps, code(ctx.act_dtype),
-                        ctx.stream),
-          "mlstm_scan", ctx.stream);
+    // Decode steps and the smallest pieces go token by token; everything else chunk by chunk.  The choice follows the step's
+    // capacity bucket alone, so that every step of a bucket asks for the same scratch.
+    if (ctx.one_token_each || ctx.T_cap <= MLSTM_SCAN_MAX_TOKENS) {
+        check(vm_mlstm_scan(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, ctx.B, H, D, V, cap, eps, code(ctx.act_dtype),
+                            ctx.stream),
+              "mlstm_scan", ctx.stream);
+        return;
+    }
+    float* scratch = static_cast<float*>(const_cast<StepContext&>(ctx).take(vm_mlstm_chunk_scratch_floats(ctx.T_cap, ctx.B_cap, H, D, V), DType::F32));
+    check(vm_mlstm_chunks(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, scratch, ctx.T, ctx.B, H, D, V, cap, eps,
+                          code(ctx.act_dtype), ctx.stream),
+          "mlstm_chunks", ctx.stream);
+    ++counters().own_launches;          // two kernels
+    const_cast<StepContext&>(ctx).give(scratch);
 }
 
 inline void expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top, int* chosen,

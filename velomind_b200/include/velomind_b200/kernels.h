@@ -53,6 +53,12 @@ int vm_mlstm_scan(const float* proj, int ld, const float* bias_i, const float* b
                   const int* cu_tokens, const int* slots, void* out, int B, int H, int D, int V, float cap, float eps, int act_dtype,
                   cudaStream_t stream);
 
+// the same recurrence chunk by chunk (prompts): scratch of vm_mlstm_chunk_scratch_floats(T, B, H, D, V) floats
+long long vm_mlstm_chunk_scratch_floats(int T, int B, int H, int D, int V);
+int vm_mlstm_chunks(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state,
+                    const int* cu_tokens, const int* slots, void* out, float* scratch, int T, int B, int H, int D, int V, float cap,
+                    float eps, int act_dtype, cudaStream_t stream);
+
 // ---- routed_experts.cu: a routed feed-forward for few tokens
 int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
                      int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream);
