@@ -247,6 +247,88 @@ def unequal_batch_run(text_engine, batch, lo, hi, decode_steps, vocab):
     return batch * tm.decode_steps / tm.decode_seconds, n_prompt / tm.prefill_seconds, n_prompt
 
 
+# ------------------------------------------------------------------------------------------------ --design kogilix
+# Layer sizes that resemble a real model's (random weights, four layers: latent attention + dense feed-forward, mLSTM + routed
+# experts, latent attention on the first layer's latents + routed experts, mLSTM + routed experts), and beside each the Llama
+# decoder of this library at equal width, depth, head count and dense feed-forward size.
+KOGILIX_SIZES = {
+    "w1024": dict(width=1024, heads=16, dim=64, q_rank=384, kv_rank=128, lstm_heads=4, lstm_dim=128, lstm_vdim=256, ff=2816,
+                  experts=16, top=4, expert_ff=512, shared_ff=1024, vocab=32000),
+    "w2048": dict(width=2048, heads=32, dim=64, q_rank=768, kv_rank=128, lstm_heads=8, lstm_dim=128, lstm_vdim=256, ff=5632,
+                  experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000),
+}
+
+
+def kogilix_config(z):
+    att = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "scale": z["dim"] ** -0.5}
+    lstm = {"heads": z["lstm_heads"], "dim": z["lstm_dim"], "vdim": z["lstm_vdim"], "gate_cap": 15.0}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
+    return {"architecture": "Kogilix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": att, "mlp": {"kind": "dense", "ff": z["ff"]}},
+                       {"type": "mlstm", "mixer": lstm, "mlp": moe},
+                       {"type": "latent_attention", "mixer": dict(att, kv_from=0), "mlp": moe},
+                       {"type": "mlstm", "mixer": lstm, "mlp": moe}]}
+
+
+def llama_config_like(z):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 4, "hidden_size": z["width"],
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["heads"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
+            "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192}
+
+
+def op_table(vm, engine, entries):
+    """Device time per kind of operation of ONE step (two events around every launch): {name: [launches, ms]}."""
+    with vm.OpTimes() as t:
+        engine.step(entries)
+        text = t.table()
+    out = {}
+    for line in text.splitlines()[1:]:
+        cells = line.split()
+        if len(cells) >= 3 and cells[0] != "total":
+            out[cells[0]] = [int(cells[1]), float(cells[2])]
+    return out
+
+
+def design_arm(args):
+    """Prompt and decode throughput of the Kogilix design at a few sizes, beside the Llama decoder at equal size."""
+    import numpy as np
+    import velomind_b200 as vm
+    T, B, prompt_len = 2048, 8, 512
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sizes = {}
+    clock = ClockSampler()
+    clock.start()
+    for name, z in KOGILIX_SIZES.items():
+        row = {}
+        for which, cfg in (("kogilix", kogilix_config(z)), ("llama", llama_config_like(z))):
+            with tempfile.TemporaryDirectory(prefix="velomind_bench_") as folder:
+                vm.write_random_model(folder, cfg, seed=0, std=0.02)
+                te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="bfloat16", max_tokens=B * 1024 + 4 * T, max_batch=B)).load()
+            fresh = vm.Engine(te.model, T + 64, use_graphs=False)
+            pms = prefill_run(fresh, T, z["vocab"])
+            rng = np.random.default_rng(3)
+            slot = fresh.open()
+            prompt_ops = op_table(vm, fresh, [vm.Entry(slot, rng.integers(0, z["vocab"], T).tolist(), [T - 1])])
+            fresh.close(slot)
+            del fresh
+            ms, _, launches, calls, _ = decode_run(te, B, prompt_len, steps, warmup, z["vocab"])
+            eng = te.engine
+            slots = [eng.open() for _ in range(B)]
+            eng.step([vm.Entry(sl, rng.integers(0, z["vocab"], prompt_len).tolist(), []) for sl in slots])
+            decode_ops = op_table(vm, eng, [vm.Entry(sl, [1], [0]) for sl in slots])
+            for sl in slots:
+                eng.close(sl)
+            row[which] = {"prefill_tokens_per_s": T * 1000.0 / pms, "prefill_ms": pms, "decode_tokens_per_s": B * 1000.0 / ms, "decode_ms_per_step": ms,
+                          "decode_launches_per_step": launches / steps, "decode_library_calls_per_step": calls / steps,
+                          "prefill_ops": prompt_ops, "decode_ops": decode_ops}
+            del te
+        sizes[name] = dict(row, config=z)
+    clocks = clock.stop()
+    return {"design": "kogilix", "metric": "prompt tok/s (one prompt of 2,048 tokens, first-seen shape) and decode tok/s (batch 8, 512 cached tokens)",
+            "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "layers": 4, "sizes": sizes,
+            "clocks": clocks, "peaks": peaks()}
+
+
 def _parse_reference_table(markdown: str):
     """Rows of the reference tool's report: {S: (prefill ms, prefill tok/s, decode ms, decode tok/s)} of the CUDA backend."""
     rows = {}
@@ -346,8 +428,17 @@ def main() -> int:
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="sizes of the random model: the benchmark's SmolLM2-135M (default), or the 360M / 1.7B shapes of the family")
+    ap.add_argument("--design", default="", choices=["", "kogilix"],
+                    help="instead of the benchmark: prompt and decode throughput of another design of the library at a few layer sizes, "
+                         "beside the Llama decoder at equal size (one JSON line of its own)")
     args = ap.parse_args()
 
+    if args.design:
+        if args.gpus != 1:
+            print(f"bench.py measures a single-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
+            return 2
+        print(json.dumps(design_arm(args)))
+        return 0
     if args.impl == "reference":
         print(json.dumps(reference_arm(args)))
         return 0

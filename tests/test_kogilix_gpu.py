@@ -134,6 +134,25 @@ def test_each_mechanism_alone(name, toy_plugin, tmp_path):
     run_cuts(engine, requests, plain, cuts, 3e-5)
 
 
+def test_experts_of_many_tokens_bfloat16(toy_plugin, tmp_path):
+    """Prompts group their (token, expert) pairs by expert and multiply on the tensor cores; decode steps stream each token's
+    experts.  Both against the plain implementation, on bfloat16-exact inputs and weights, so that the routing is the same."""
+    import velomind_b200 as vm
+    args = {"hidden": 64, "experts": 6, "top": 2, "ff": 32, "shared_ff": 40}
+    cfg = probe_config(64, ff_block("routed_experts", args))
+    w = rounded_to_bf16(random_tensors(vm.weight_table(cfg), np.random.default_rng(31), 0.25))
+    folder = write_model(str(tmp_path / "grouped"), cfg, w, as_bf16=True)
+    engine = vm.Engine(vm.load_model(folder, "bfloat16", "cuda:0"), 64 * 12, max_slots=3)
+    requests = S.make_requests(64, (130, 70, 300, 65), seed=4)
+    mlp = {"router": {"top": 2}, "shared": {"ff": 40}}
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks]
+        plain[rid] = x + K.routed_experts(x, w, "layers.0.feed_forward.", mlp)
+    cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests, tail=20), "batches": S.steps_unequal_batches(requests)}
+    run_cuts(engine, requests, plain, cuts, 1.5e-2)
+
+
 # ----------------------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def kog_folders(tmp_path_factory):
@@ -208,6 +227,15 @@ def far_key_model(tmp_path, vm):
     m = w[p + "uq"].astype(np.float64) @ (w[p + "dq.norm"].astype(np.float64)[:, None] * w[p + "dq"].astype(np.float64))
     w["embed.weight"][ask] = np.linalg.lstsq(m, k_far, rcond=None)[0].astype(np.float32)
     w = rounded_to_bf16(w)                             # both precisions then run the very same numbers
+    # the design's score scale is a constant of the configuration: large enough that the far key outweighs 700 others together
+    e = w["embed.weight"].astype(np.float64)
+    q = K.lin(K.rms_norm(K.lin(e[ask][None], w[p + "dq"]), w[p + "dq.norm"], args["eps"]), w[p + "uq"]).reshape(args["heads"], args["dim"])
+    k = K.lin(K.latent_of(e, w, p, args["eps"]), w[p + "uk"]).reshape(64, args["heads"], args["dim"])
+    s_all = np.einsum("hd,nhd->hn", q, k)
+    others = np.delete(s_all, [far, ask], axis=1)
+    args["scale"] = float(np.ceil(10.0 / (s_all[:, far] - others.max(axis=1)).min()))
+    assert 0 < args["scale"] < 200
+    cfg = probe_config(64, mixer_block("latent_attention", args), limit=2048)
     return {"float32": write_model(str(tmp_path / "far32"), cfg, w), "bfloat16": write_model(str(tmp_path / "far16"), cfg, w, as_bf16=True)}, args, w, far, ask
 
 

@@ -1,0 +1,222 @@
+// A routed feed-forward (mixture of experts) for many tokens: the (token, expert) pairs are grouped by expert on the device
+// and each expert multiplies only the rows that chose it.
+//
+//   group:    count the pairs of every expert, give each expert a run of rows padded to whole tiles of 64, and place every
+//             pair in its expert's run.  Everything stays on the device: the launches that follow have a fixed shape
+//             (the step's capacity), and tiles without an expert return at once.
+//   up:       act[row, :] = activation(W_up[e] x[token(row)])          bf16 tensor-core tiles (mma.sync m16n8k16), rows gathered
+//   down:     y[row, :] = W_down[e] act[row, :]                         float32 result
+//   combine:  out[t] = sum_k w[t, k] y[row(t, k)] (+ gate[t] * shared[t])   in the order of the token's ranks: deterministic
+//
+// Which row of its run a pair gets depends on the order in which threads arrive, but no result depends on the row.
+#include "mma.cuh"
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 32, PAD = 8;       // tile of rows, of columns, of the summed dimension; padding of a shared-memory row
+constexpr int GROUP_THREADS = 1024;
+
+__device__ __forceinline__ float act_of(float z, int kind) {
+    if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
+// one block: counts, padded offsets, placement.  row_of_pair [T * top]; token_of_row [row_cap] (-1: padding); expert_of_tile [row_cap / TM] (-1: unused)
+__global__ void group_pairs_kernel(const int* __restrict__ chosen, int n_pairs, int top, int E, int row_cap, int* __restrict__ row_of_pair,
+                                   int* __restrict__ token_of_row, int* __restrict__ expert_of_tile) {
+    extern __shared__ int sh[];            // [E] counts, [E] cursors
+    int* count = sh;
+    int* cursor = sh + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < row_cap; i += blockDim.x) token_of_row[i] = -1;
+    for (int i = threadIdx.x; i < row_cap / TM; i += blockDim.x) expert_of_tile[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            const int tiles = (count[e] + TM - 1) / TM;
+            cursor[e] = at;
+            for (int k = 0; k < tiles; ++k) expert_of_tile[at / TM + k] = e;
+            at += tiles * TM;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e < 0 || e >= E) { row_of_pair[i] = -1; continue; }
+        const int row = atomicAdd(&cursor[e], 1);
+        row_of_pair[i] = row;
+        token_of_row[row] = i / top;
+    }
+}
+
+// C[TM, TN] tile of A[rows, K] B[e][N, K]^T; 4 warps, each 32 x 32.  A rows come from `a_row(r)` (a pointer or null for a zero row).
+template <typename ARow, typename Epilogue>
+__device__ __forceinline__ void tile_product(ARow a_row, const __nv_bfloat16* __restrict__ B, int N, int K, int n0, Epilogue epilogue) {
+    __shared__ __align__(16) __nv_bfloat16 As[TM][TK + PAD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[TN][TK + PAD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+    // each thread moves two 16-byte pieces of each operand per step: rows tid / 4 and tid / 4 + 32, piece tid % 4
+    const int lr = tid >> 2, lp = (tid & 3) * 8;
+    const __nv_bfloat16* a_src[2] = {a_row(lr), a_row(lr + 32)};
+    const __nv_bfloat16* b_src[2] = {n0 + lr < N ? B + (size_t)(n0 + lr) * K : nullptr, n0 + lr + 32 < N ? B + (size_t)(n0 + lr + 32) * K : nullptr};
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int k0 = 0; k0 < K; k0 += TK) {
+        uint4 av[2], bv[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            av[i] = a_src[i] ? *reinterpret_cast<const uint4*>(a_src[i] + k0 + lp) : zero;
+            bv[i] = b_src[i] ? *reinterpret_cast<const uint4*>(b_src[i] + k0 + lp) : zero;
+        }
+        __syncthreads();                   // the previous step's fragments are read
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            *reinterpret_cast<uint4*>(&As[lr + 32 * i][lp]) = av[i];
+            *reinterpret_cast<uint4*>(&Bs[lr + 32 * i][lp]) = bv[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; kk += 16) {
+            unsigned a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + 16 * i + g;
+                a[i][0] = *reinterpret_cast<const unsigned*>(&As[r][kk + 2 * t]);
+                a[i][1] = *reinterpret_cast<const unsigned*>(&As[r + 8][kk + 2 * t]);
+                a[i][2] = *reinterpret_cast<const unsigned*>(&As[r][kk + 2 * t + 8]);
+                a[i][3] = *reinterpret_cast<const unsigned*>(&As[r + 8][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = wn + 8 * j + g;
+                b[j][0] = *reinterpret_cast<const unsigned*>(&Bs[n][kk + 2 * t]);
+                b[j][1] = *reinterpret_cast<const unsigned*>(&Bs[n][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) vm_mma_bf16_16816(acc[i][j], a[i][0], a[i][1], a[i][2], a[i][3], b[j][0], b[j][1]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = wm + 16 * i + g, n = n0 + wn + 8 * j + 2 * t;
+            epilogue(r, n, acc[i][j][0], acc[i][j][1]);
+            epilogue(r + 8, n, acc[i][j][2], acc[i][j][3]);
+        }
+}
+
+__global__ void __launch_bounds__(128)
+experts_up_grouped_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_up, const int* __restrict__ token_of_row,
+                          const int* __restrict__ expert_of_tile, int hidden, int ff, int act_kind, __nv_bfloat16* __restrict__ act) {
+    const int e = expert_of_tile[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+    auto a_row = [&](int r) -> const __nv_bfloat16* {
+        const int tok = token_of_row[row0 + r];
+        return tok >= 0 ? x + (size_t)tok * hidden : nullptr;
+    };
+    tile_product(a_row, w_up + (size_t)e * ff * hidden, ff, hidden, n0, [&](int r, int n, float c0, float c1) {
+        __nv_bfloat16* dst = act + (size_t)(row0 + r) * ff + n;
+        if (n + 1 < ff) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(act_of(c0, act_kind), act_of(c1, act_kind));
+        else if (n < ff) dst[0] = __float2bfloat16_rn(act_of(c0, act_kind));
+    });
+}
+
+__global__ void __launch_bounds__(128)
+experts_down_grouped_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down, const int* __restrict__ expert_of_tile,
+                            int hidden, int ff, float* __restrict__ y) {
+    const int e = expert_of_tile[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+    auto a_row = [&](int r) -> const __nv_bfloat16* { return act + (size_t)(row0 + r) * ff; };
+    tile_product(a_row, w_down + (size_t)e * hidden * ff, hidden, ff, n0, [&](int r, int n, float c0, float c1) {
+        float* dst = y + (size_t)(row0 + r) * hidden + n;
+        if (n + 1 < hidden) *reinterpret_cast<float2*>(dst) = make_float2(c0, c1);
+        else if (n < hidden) dst[0] = c0;
+    });
+}
+
+__global__ void experts_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
+                                       const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int T, int hidden, int top,
+                                       __nv_bfloat16* __restrict__ out) {
+    const size_t n = (size_t)T * hidden;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / hidden), c = (int)(i - (size_t)t * hidden);
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = row_of_pair[(size_t)t * top + k];
+            if (row >= 0) acc = fmaf(weight[(size_t)t * top + k], y[(size_t)row * hidden + c], acc);
+        }
+        if (shared_y) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared_y[i], acc);
+        out[i] = __float2bfloat16_rn(acc);
+    }
+}
+
+template <typename T> __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int kind) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = vm_from_float<T>(act_of(vm_to_float(in[i]), kind));
+}
+
+}  // namespace
+
+// rows the grouped layout may need for T tokens: every pair, plus padding of each expert's run to whole tiles
+VM_API long long vm_experts_grouped_rows(int T, int top, int E) { return ((long long)T * top + (long long)E * (TM - 1) + TM - 1) / TM * TM; }
+
+// x, out [T, hidden] bfloat16; w_up [E * ff, hidden], w_down [E * hidden, ff] bfloat16; chosen / weight [T, top];
+// scratch: row_of_pair int [T * top], token_of_row int [row_cap], expert_of_tile int [row_cap / 64], act bf16 [row_cap, ff],
+// y float32 [row_cap, hidden]; shared_y float32 [T, hidden] (or null) is added times shared_gate [T] (or 1).
+// hidden and ff must be multiples of 32.
+VM_API int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                              const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                              int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hidden % TK || ff % TK || top <= 0 || E <= 0) return VM_ERR_UNSUPPORTED;
+    if (row_cap % TM || row_cap < vm_experts_grouped_rows(T, top, E)) return VM_ERR_BAD_ARG;
+    if ((size_t)2 * E * sizeof(int) > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, row_of_pair, token_of_row,
+                                                                                  expert_of_tile);
+    int st = vm_launch_status();
+    if (st) return st;
+    // tiles the step can need at most (the capacity may be larger)
+    const int tiles = (int)(vm_experts_grouped_rows(T, top, E) / TM);
+    experts_up_grouped_kernel<<<dim3(tiles, (ff + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_up, token_of_row,
+                                                                                  expert_of_tile, hidden, ff, act_kind, (__nv_bfloat16*)act);
+    st = vm_launch_status();
+    if (st) return st;
+    experts_down_grouped_kernel<<<dim3(tiles, (hidden + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down,
+                                                                                        expert_of_tile, hidden, ff, y);
+    st = vm_launch_status();
+    if (st) return st;
+    const size_t n = (size_t)T * hidden;
+    const size_t want = (n + 255) / 256;
+    experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, weight, shared_y, shared_gate, T, hidden, top,
+                                                                                         (__nv_bfloat16*)out);
+    return vm_launch_status();
+}
+
+VM_API int vm_activation(const void* in, void* out, long long n, int kind, int act_dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const size_t want = ((size_t)n + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (act_dtype == VM_F32) activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, (size_t)n, kind);
+    else if (act_dtype == VM_BF16) activation_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, (size_t)n, kind);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}

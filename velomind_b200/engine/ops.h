@@ -137,6 +137,21 @@ inline void experts_few_tokens(const void* x, const DeviceTensor& up, const Devi
     ++counters().own_launches;          // two kernels
 }
 
+inline void activation(const void* in, void* out, long long n, int kind, DType act, cudaStream_t s) {
+    Timed t("activation", s);
+    check(vm_activation(in, out, n, kind, code(act), s), "activation", s);
+}
+
+inline void experts_grouped(const void* x, const DeviceTensor& up, const DeviceTensor& down, const int* chosen, const float* weight, const float* shared_y,
+                            const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                            int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t s) {
+    Timed t("experts_grouped", s);
+    check(vm_experts_grouped(x, up.ptr, down.ptr, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, E, act_kind, row_cap, row_of_pair,
+                             token_of_row, expert_of_tile, act, y, out, s),
+          "experts_grouped", s);
+    counters().own_launches += 3;       // four kernels
+}
+
 // out = x W^T.  x [T, K] (row stride ldx), W [N, K], out [T, N]; a library matrix product, as in the reference
 // (src/cuda/ops/matmul.cu:87-126); float32 runs without any reduced-precision mode.
 void linear(const void* x, DType x_dtype, long long ldx, const DeviceTensor& W, void* out, DType out_dtype, int T, cudaStream_t s);

@@ -92,6 +92,13 @@ int vm_attention_decode_bf16(const void* q, int q_row_stride, const void* kpages
                              int max_blocks, const int* positions, void* out, float* partial, int* counters, int B, int H,
                              int Hkv, int D, int n_splits, float scale, int window, int n_pages, int* err, cudaStream_t stream);
 
+// ---- routed_experts_grouped.cu: the same feed-forward for many tokens (bfloat16), pairs grouped by expert on the device
+long long vm_experts_grouped_rows(int T, int top, int E);
+int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                       const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                       int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream);
+int vm_activation(const void* in, void* out, long long n, int kind, int act_dtype, cudaStream_t stream);
+
 // ---- skinny_gemm.cu: weight-streaming products for few rows (bfloat16 weights [N, K])
 // (err: the step's error word, may be null; the kernel for large weight matrices reports a wait that ran out there)
 int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K, void* out,

@@ -74,6 +74,38 @@ public:
         ops::expert_router(x, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
                            gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
                            ctx.stream);
+        // Many tokens (by the step's capacity, so that a bucket's steps ask for the same scratch): pairs grouped by expert, tensor-core
+        // tiles per expert, the shared expert as two library products.  Few tokens: every token streams the rows of its experts.
+        if (ctx.act_dtype == DType::BF16 && up_.dtype == DType::BF16 && hidden_ % 32 == 0 && ff_ % 32 == 0 && ctx.T_cap > GROUPED_FROM_TOKENS &&
+            !ctx.one_token_each) {
+            float* shared_y = nullptr;
+            if (sff_ > 0) {
+                void* u = ctx.take_tokens(sff_, DType::BF16);
+                ops::linear(x, DType::BF16, hidden_, s_up_, u, DType::BF16, ctx.T, ctx.stream);
+                ops::activation(u, u, static_cast<long long>(ctx.T) * sff_, sact_, DType::BF16, ctx.stream);
+                shared_y = static_cast<float*>(ctx.take_tokens(hidden_, DType::F32));
+                ops::linear(u, DType::BF16, sff_, s_down_, shared_y, DType::F32, ctx.T, ctx.stream);
+                ctx.give(u);
+            }
+            const int row_cap = static_cast<int>(vm_experts_grouped_rows(ctx.T_cap, top_, E_));
+            int* row_of_pair = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
+            int* token_of_row = static_cast<int*>(ctx.take(row_cap, DType::I32));
+            int* expert_of_tile = static_cast<int*>(ctx.take(row_cap / 64, DType::I32));
+            void* act = ctx.take(static_cast<long long>(row_cap) * ff_, DType::BF16);
+            float* y = static_cast<float*>(ctx.take(static_cast<long long>(row_cap) * hidden_, DType::F32));
+            ops::experts_grouped(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, E_, act_, row_cap, row_of_pair, token_of_row,
+                                 expert_of_tile, act, y, out, ctx.stream);
+            ctx.give(y);
+            ctx.give(act);
+            ctx.give(expert_of_tile);
+            ctx.give(token_of_row);
+            ctx.give(row_of_pair);
+            ctx.give(shared_y);
+            ctx.give(sgate);
+            ctx.give(weight);
+            ctx.give(chosen);
+            return;
+        }
         void* act = ctx.take_tokens(static_cast<long long>(top_) * ff_ + sff_, ctx.act_dtype);
         ops::experts_few_tokens(x, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T, hidden_,
                                 ff_, sff_, top_, act_, sact_, act, out, ctx.act_dtype, ctx.stream);
@@ -82,6 +114,8 @@ public:
         ctx.give(weight);
         ctx.give(chosen);
     }
+
+    static constexpr int GROUPED_FROM_TOKENS = 64;      // a step's capacity above which the pairs are grouped by expert
 
 private:
     int hidden_, E_, top_, ff_, act_, sff_, sact_;
