@@ -258,7 +258,8 @@ def test_a_far_key_decides(place, toy_plugin, tmp_path):
         engine = vm.Engine(vm.load_model(folders[dtype], dtype, "cuda:0"), 64 * 12)
         whole = [{"step": 0, "entries": [{"id": "r", "tokens": toks, "want": [n - 1]}], "end": ["r"]}]
         decoded = [{"step": 0, "entries": [{"id": "r", "tokens": toks[:-3], "want": []}], "end": []}] + \
-                  [{"step": 1 + j, "entries": [{"id": "r", "tokens": [toks[n - 3 + j]], "want": [0]}], "end": ["r"] if j == 2 else []} for j in range(3)]
+                  [{"step": 1 + j, "entries": [{"id": "r", "tokens": [toks[n - 3 + j]], "want": [0] if j == 2 else []}], "end": ["r"] if j == 2 else []}
+                   for j in range(3)]        # (only the asking token: at this score scale the others' answers are not stable under bfloat16)
         run_cuts(engine, requests, plain, {"whole": whole, "decoded": decoded}, tol)
 
 

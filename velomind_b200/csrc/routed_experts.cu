@@ -22,6 +22,22 @@ __device__ __forceinline__ float expert_act(float z, int kind) {
 // dot product of a weight row with a float32 vector in shared memory, summed over a warp
 template <typename W> __device__ __forceinline__ float warp_dot(const W* __restrict__ w, const float* __restrict__ x, int n, int lane) {
     float acc = 0.f;
+    if ((n & 3) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        float acc1 = 0.f;
+        int i = lane;
+        for (; i + 32 < n / 4; i += 64) {              // two independent loads in flight
+            const float4 a = w4[i], b = w4[i + 32], xa = x4[i], xb = x4[i + 32];
+            acc = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, acc))));
+            acc1 = fmaf(b.x, xb.x, fmaf(b.y, xb.y, fmaf(b.z, xb.z, fmaf(b.w, xb.w, acc1))));
+        }
+        if (i < n / 4) {
+            const float4 a = w4[i], xa = x4[i];
+            acc = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, acc))));
+        }
+        return vm_warp_sum(acc + acc1);
+    }
     for (int i = lane; i < n; i += 32) acc = fmaf(vm_to_float(w[i]), x[i], acc);
     return vm_warp_sum(acc);
 }
@@ -29,8 +45,10 @@ template <> __device__ __forceinline__ float warp_dot<__nv_bfloat16>(const __nv_
     float acc = 0.f;
     if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         const uint4* w8 = reinterpret_cast<const uint4*>(w);
+        uint4 p = make_uint4(0, 0, 0, 0), nxt = lane < n / 8 ? w8[lane] : p;
         for (int i = lane; i < n / 8; i += 32) {
-            const uint4 p = w8[i];
+            p = nxt;
+            if (i + 32 < n / 8) nxt = w8[i + 32];       // the next piece is on its way while this one is summed
             const unsigned u[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -51,7 +69,7 @@ template <typename T>
 __global__ void router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ b_router,
                               const float* __restrict__ w_gate, int hidden, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
                               float* __restrict__ shared_gate) {
-    extern __shared__ float sm[];          // [hidden] input, [E] logits
+    extern __shared__ __align__(16) float sm[];          // [hidden] input, [E] logits
     float* xs = sm;
     float* z = sm + hidden;
     vm_pdl_launch_dependents();
@@ -106,7 +124,7 @@ template <typename T, typename W>
 __global__ void experts_up_kernel(const T* __restrict__ x, const W* __restrict__ w_up, const W* __restrict__ w_up_shared,
                                   const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared,
                                   T* __restrict__ act) {
-    extern __shared__ float xs[];          // [hidden]
+    extern __shared__ __align__(16) float xs[];          // [hidden]
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -135,7 +153,7 @@ template <typename T, typename W>
 __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restrict__ w_down, const W* __restrict__ w_down_shared,
                                     const int* __restrict__ chosen, const float* __restrict__ weight, const float* __restrict__ shared_gate,
                                     int hidden, int ff, int ff_shared, int top, T* __restrict__ out) {
-    extern __shared__ float as[];          // [top * ff + ff_shared]
+    extern __shared__ __align__(16) float as[];          // [top * ff + ff_shared]
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -182,10 +200,10 @@ VM_API int vm_expert_router(const void* x, const float* w_router, const float* b
     const size_t smem = (size_t)(hidden + E) * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32)
-        vm_launch_pdl(router_kernel<float>, dim3(T), dim3(128), smem, stream, (const float*)x, w_router, b_router, w_gate, hidden, E, top, chosen, weight,
+        vm_launch_pdl(router_kernel<float>, dim3(T), dim3(256), smem, stream, (const float*)x, w_router, b_router, w_gate, hidden, E, top, chosen, weight,
                       shared_gate);
     else if (act_dtype == VM_BF16)
-        vm_launch_pdl(router_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, (const __nv_bfloat16*)x, w_router, b_router, w_gate, hidden, E, top,
+        vm_launch_pdl(router_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, (const __nv_bfloat16*)x, w_router, b_router, w_gate, hidden, E, top,
                       chosen, weight, shared_gate);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();

@@ -105,20 +105,30 @@ inline void mlstm_scan(const float* proj, int ld, const float* bias_i, const flo
                        int D, int V, float cap, float eps) {
     Timed t("mlstm_scan", ctx.stream);
     if (!ctx.state() || ctx.state_floats() != H * (D * V + D + 1)) throw CacheError("mlstm: the cache holds no state area of this layer's size");
-    // Decode steps and the smallest pieces go token by token; everything else chunk by chunk.  The choice follows the step's
-    // capacity bucket alone, so that every step of a bucket asks for the same scratch.
-    if (ctx.one_token_each || ctx.T_cap <= MLSTM_SCAN_MAX_TOKENS) {
+    // Decode steps stream the state once; the smallest pieces go token by token; everything else chunk by chunk.  The choice
+    // follows the step's capacity bucket alone, so that every step of a bucket asks for the same scratch.
+    StepContext& c = const_cast<StepContext&>(ctx);
+    if (ctx.one_token_each) {
+        float* scratch = static_cast<float*>(c.take(static_cast<long long>(ctx.B_cap) * H * (V + D + 1), DType::F32));
+        check(vm_mlstm_step(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, scratch, ctx.B, H, D, V, cap, eps,
+                            code(ctx.act_dtype), ctx.stream),
+              "mlstm_step", ctx.stream);
+        ++counters().own_launches;      // two kernels
+        c.give(scratch);
+        return;
+    }
+    if (ctx.T_cap <= MLSTM_SCAN_MAX_TOKENS) {
         check(vm_mlstm_scan(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, ctx.B, H, D, V, cap, eps, code(ctx.act_dtype),
                             ctx.stream),
               "mlstm_scan", ctx.stream);
         return;
     }
-    float* scratch = static_cast<float*>(const_cast<StepContext&>(ctx).take(vm_mlstm_chunk_scratch_floats(ctx.T_cap, ctx.B_cap, H, D, V), DType::F32));
+    float* scratch = static_cast<float*>(c.take(vm_mlstm_chunk_scratch_floats(ctx.T_cap, ctx.B_cap, H, D, V), DType::F32));
     check(vm_mlstm_chunks(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, scratch, ctx.T, ctx.B, H, D, V, cap, eps,
                           code(ctx.act_dtype), ctx.stream),
           "mlstm_chunks", ctx.stream);
-    ++counters().own_launches;          // two kernels
-    const_cast<StepContext&>(ctx).give(scratch);
+    counters().own_launches += 3;       // four kernels
+    c.give(scratch);
 }
 
 inline void expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top, int* chosen,

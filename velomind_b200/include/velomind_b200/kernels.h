@@ -58,6 +58,10 @@ long long vm_mlstm_chunk_scratch_floats(int T, int B, int H, int D, int V);
 int vm_mlstm_chunks(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state,
                     const int* cu_tokens, const int* slots, void* out, float* scratch, int T, int B, int H, int D, int V, float cap,
                     float eps, int act_dtype, cudaStream_t stream);
+// one token per sequence (token s belongs to sequence s): scratch of B * H * (V + D + 1) floats
+int vm_mlstm_step(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state,
+                  const int* cu_tokens, const int* slots, void* out, float* scratch, int B, int H, int D, int V, float cap, float eps,
+                  int act_dtype, cudaStream_t stream);
 
 // ---- routed_experts.cu: a routed feed-forward for few tokens
 int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
