@@ -4,8 +4,8 @@
 //   w = softmax over the chosen logits only
 //   y = sum_k w_k  W_down[e_k] act(W_up[e_k] x)   (+ s * W_down_shared act(W_up_shared x),  s = sigmoid(w_sg . x))
 //
-// Three launches: the router (a block per token), the up-projections with their activation (a warp per row of the token's
-// virtual matrix [top * ff + ff_shared, hidden]), the down-projections with the weighted sum (a warp per output column; the
+// Three launches: the router (a block per token), the up-projections with their activation (a warp per four rows of the token's
+// virtual matrix [top * ff + ff_shared, hidden]), the down-projections with the weighted sum (a warp per four output columns; the
 // experts are added in the order of their rank, so a token's result does not depend on the batch it is in).
 // Experts have no biases.  Weights are float32 or bfloat16 (template W), activations float32 or bfloat16 (template T);
 // all sums are float32.
@@ -62,6 +62,46 @@ template <> __device__ __forceinline__ float warp_dot<__nv_bfloat16>(const __nv_
     }
     return vm_warp_sum(acc);
 }
+
+// R rows at once against the same vector: the rows' loads are independent and in flight together
+template <typename W, int R>
+__device__ __forceinline__ void warp_dot_rows(const W* const (&w)[R], const float* __restrict__ x, int n, int lane, float (&out)[R]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = 0.f;
+    bool vec = (n & 7) == 0 && sizeof(W) == 2;
+#pragma unroll
+    for (int r = 0; r < R; ++r) vec = vec && (reinterpret_cast<uintptr_t>(w[r]) & 15) == 0;
+    if (vec) {
+        for (int i = lane; i < n / 8; i += 32) {
+            uint4 p[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) p[r] = reinterpret_cast<const uint4*>(w[r])[i];
+            float xv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) xv[k] = x[i * 8 + k];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const unsigned u[4] = {p[r].x, p[r].y, p[r].z, p[r].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+                    out[r] = fmaf(__low2float(b), xv[2 * k], out[r]);
+                    out[r] = fmaf(__high2float(b), xv[2 * k + 1], out[r]);
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            const float xi = x[i];
+#pragma unroll
+            for (int r = 0; r < R; ++r) out[r] = fmaf(vm_to_float(w[r][i]), xi, out[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = vm_warp_sum(out[r]);
+}
+
+constexpr int ROWS_PER_WARP = 4;
 
 // ------------------------------------------------------------------------------------------------ router
 // Router weights, bias and the shared expert's gate row are float32 (exact copies of what the checkpoint stores).
@@ -131,20 +171,29 @@ __global__ void experts_up_kernel(const T* __restrict__ x, const W* __restrict__
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(x[(size_t)t * hidden + i]);
     __syncthreads();
     const int rows = top * ff + ff_shared;
-    const int r = blockIdx.x * nw + warp;
-    if (r >= rows) return;
-    const W* wrow;
-    int kind;
-    if (r < top * ff) {
-        const int e = chosen[(size_t)t * top + r / ff];
-        wrow = w_up + ((size_t)e * ff + r % ff) * hidden;
-        kind = act_kind;
-    } else {
-        wrow = w_up_shared + (size_t)(r - top * ff) * hidden;
-        kind = act_kind_shared;
+    const int r0 = (blockIdx.x * nw + warp) * ROWS_PER_WARP;
+    if (r0 >= rows) return;
+    const W* wrow[ROWS_PER_WARP];
+    int kind[ROWS_PER_WARP];
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_WARP; ++i) {
+        const int r = min(r0 + i, rows - 1);              // (a row past the end repeats the last one and is not stored)
+        if (r < top * ff) {
+            const int e = chosen[(size_t)t * top + r / ff];
+            wrow[i] = w_up + ((size_t)e * ff + r % ff) * hidden;
+            kind[i] = act_kind;
+        } else {
+            wrow[i] = w_up_shared + (size_t)(r - top * ff) * hidden;
+            kind[i] = act_kind_shared;
+        }
     }
-    const float d = warp_dot<W>(wrow, xs, hidden, lane);
-    if (lane == 0) act[(size_t)t * rows + r] = vm_from_float<T>(expert_act(d, kind));
+    float d[ROWS_PER_WARP];
+    warp_dot_rows<W, ROWS_PER_WARP>(wrow, xs, hidden, lane, d);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i)
+            if (r0 + i < rows) act[(size_t)t * rows + r0 + i] = vm_from_float<T>(expert_act(d[i], kind[i]));
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ down-projections
@@ -160,18 +209,33 @@ __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restri
     const int rows = top * ff + ff_shared;
     for (int i = threadIdx.x; i < rows; i += blockDim.x) as[i] = vm_to_float(act[(size_t)t * rows + i]);
     __syncthreads();
-    const int c = blockIdx.x * nw + warp;
-    if (c >= hidden) return;
-    float y = 0.f;
+    const int c0 = (blockIdx.x * nw + warp) * ROWS_PER_WARP;
+    if (c0 >= hidden) return;
+    float y[ROWS_PER_WARP] = {};
+    const W* wrow[ROWS_PER_WARP];
+    float d[ROWS_PER_WARP];
     for (int k = 0; k < top; ++k) {
         const int e = chosen[(size_t)t * top + k];
-        y = fmaf(weight[(size_t)t * top + k], warp_dot<W>(w_down + ((size_t)e * hidden + c) * ff, as + k * ff, ff, lane), y);
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) wrow[i] = w_down + ((size_t)e * hidden + min(c0 + i, hidden - 1)) * ff;
+        warp_dot_rows<W, ROWS_PER_WARP>(wrow, as + k * ff, ff, lane, d);
+        const float wk = weight[(size_t)t * top + k];
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) y[i] = fmaf(wk, d[i], y[i]);
     }
     if (ff_shared > 0) {
-        const float d = warp_dot<W>(w_down_shared + (size_t)c * ff_shared, as + top * ff, ff_shared, lane);
-        y = fmaf(shared_gate ? shared_gate[t] : 1.0f, d, y);
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) wrow[i] = w_down_shared + (size_t)min(c0 + i, hidden - 1) * ff_shared;
+        warp_dot_rows<W, ROWS_PER_WARP>(wrow, as + top * ff, ff_shared, lane, d);
+        const float g = shared_gate ? shared_gate[t] : 1.0f;
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) y[i] = fmaf(g, d[i], y[i]);
     }
-    if (lane == 0) out[(size_t)t * hidden + c] = vm_from_float<T>(y);
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i)
+            if (c0 + i < hidden) out[(size_t)t * hidden + c0 + i] = vm_from_float<T>(y[i]);
+    }
 }
 
 template <typename T, typename W>
@@ -181,11 +245,12 @@ int launch_experts(const void* x, const void* w_up, const void* w_down, const vo
     const int rows = top * ff + ff_shared;
     const int warps = 8;
     if ((size_t)hidden * sizeof(float) > 48 * 1024 || (size_t)rows * sizeof(float) > 48 * 1024) return VM_ERR_UNSUPPORTED;
-    vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + warps - 1) / warps, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, (const T*)x,
+    const int per_block = warps * ROWS_PER_WARP;
+    vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, (const T*)x,
                   (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, (T*)act);
     int st = vm_launch_status();
     if (st) return st;
-    vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + warps - 1) / warps, T_), dim3(warps * 32), (size_t)rows * sizeof(float), stream,
+    vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)rows * sizeof(float), stream,
                   (const T*)act, (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, (T*)out);
     return vm_launch_status();
 }

@@ -11,6 +11,7 @@
 // (query heads that share a kv head), so prompts and decode steps use the same kernels as grouped-query attention.
 //
 // A layer may read another run's latents (the schedule's `cache_of`): it then has no W_dkv of its own, and writes nothing.
+#include <algorithm>
 #include <cmath>
 
 #include "args.h"
@@ -63,6 +64,63 @@ public:
         return n;
     }
 
+    // Few tokens (decode steps) in bfloat16: the weight-streaming products of this library, with the layer's norm taken into
+    // the down-projection and the residual sum into the output projection.
+    int max_rows() const {
+        long long most = std::max(down_.weight.rows() * down_.weight.cols(), out_.weight.rows() * out_.weight.cols());
+        most = std::max(most, up_q_.weight.rows() * up_q_.weight.cols());
+        return std::min(ops::skinny_max_rows(2 * most), ops::SKINNY_NORM_ROWS);
+    }
+
+    bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
+        const float* nw;
+        float eps;
+        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16 || ctx.T_cap > max_rows()) return false;
+        if (down_.weight.dtype != DType::BF16 || up_q_.weight.dtype != DType::BF16 || out_.weight.dtype != DType::BF16) return false;
+        return hidden_ % 32 == 0 && Rq_ % 32 == 0 && (H_ * V_) % 32 == 0 && (Rq_ + (own_ ? Rkv_ : 0)) % 8 == 0 && (H_ * D_) % 8 == 0 && hidden_ % 8 == 0;
+    }
+
+    void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
+        const float* nw = nullptr;
+        float eps = 0.f;
+        norm.as_rms(&nw, &eps);
+        KVView kv = ctx.kv();
+        if (kv.owns != own_) throw ConfigError("a latent-attention layer and its schedule disagree about whose latents it reads");
+        const int down_cols = Rq_ + (own_ ? Rkv_ : 0);
+        float* down = static_cast<float*>(ctx.take_tokens(down_cols, DType::F32));
+        ops::skinny_linear(h, nw, eps, down_.weight, ctx.T, down, down_cols, true, nullptr, ctx.err, ctx.stream);
+        void* cq = ctx.take_tokens(Rq_, DType::BF16);
+        ops::latent_norm_write(down, down_cols, Rq_, Rkv_, static_cast<const float*>(q_norm_.ptr), own_ ? static_cast<const float*>(kv_norm_.ptr) : nullptr,
+                               eps_, cq, ctx, kv, own_);
+        ctx.give(down);
+        void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
+        ops::skinny_linear(cq, nullptr, 0.f, up_q_.weight, ctx.T, q, H_ * D_, false, nullptr, ctx.err, ctx.stream);
+        ctx.give(cq);
+        void* o = attend(ctx, q, kv);
+        ops::skinny_linear(o, nullptr, 0.f, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
+        ctx.give(o);
+    }
+
+    // q [T, H*D] -> o [T, H*V] (a buffer the caller gives back); q is given back here
+    void* attend(StepContext& ctx, void* q, KVView kv) {
+        const DType act = ctx.act_dtype;
+        // the key up-projection on the query's side: qa_h = W_uk,h^T q_h
+        void* qa = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
+        ops::linear_batched(q, static_cast<long long>(H_) * D_, D_, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
+                            static_cast<long long>(H_) * Rkv_, Rkv_, act, ctx.T, Rkv_, D_, H_, ctx.stream);
+        ctx.give(q);
+        void* att = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
+        kv.v_pages = kv.k_pages;
+        ops::attention(ctx, qa, H_ * Rkv_, kv, att, H_, 1, Rkv_, scale_, 0);
+        ctx.give(qa);
+        // the value up-projection on the output's side: o_h = W_uv,h (sum_j p_j c_j)
+        void* o = ctx.take_tokens(static_cast<long long>(H_) * V_, act);
+        ops::linear_batched(att, static_cast<long long>(H_) * Rkv_, Rkv_, up_v_.ptr, static_cast<long long>(V_) * Rkv_, /*w_is_k_by_n=*/false, o,
+                            static_cast<long long>(H_) * V_, V_, act, ctx.T, V_, Rkv_, H_, ctx.stream);
+        ctx.give(att);
+        return o;
+    }
+
     void forward(StepContext& ctx, const void* x, void* out) override {
         const DType act = ctx.act_dtype;
         KVView kv = ctx.kv();
@@ -79,20 +137,7 @@ public:
         void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, act);
         up_q_.apply(ctx, cq, act, q, act, ctx.T, ctx.T_cap);
         ctx.give(cq);
-        // the key up-projection on the query's side: qa_h = W_uk,h^T q_h
-        void* qa = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
-        ops::linear_batched(q, static_cast<long long>(H_) * D_, D_, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
-                            static_cast<long long>(H_) * Rkv_, Rkv_, act, ctx.T, Rkv_, D_, H_, ctx.stream);
-        ctx.give(q);
-        void* att = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
-        kv.v_pages = kv.k_pages;
-        ops::attention(ctx, qa, H_ * Rkv_, kv, att, H_, 1, Rkv_, scale_, 0);
-        ctx.give(qa);
-        // the value up-projection on the output's side: o_h = W_uv,h (sum_j p_j c_j)
-        void* o = ctx.take_tokens(static_cast<long long>(H_) * V_, act);
-        ops::linear_batched(att, static_cast<long long>(H_) * Rkv_, Rkv_, up_v_.ptr, static_cast<long long>(V_) * Rkv_, /*w_is_k_by_n=*/false, o,
-                            static_cast<long long>(H_) * V_, V_, act, ctx.T, V_, Rkv_, H_, ctx.stream);
-        ctx.give(att);
+        void* o = attend(ctx, q, kv);
         out_.apply(ctx, o, act, out, act, ctx.T, ctx.T_cap);
         ctx.give(o);
     }

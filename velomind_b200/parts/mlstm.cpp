@@ -5,6 +5,8 @@
 // carried from step to step.  The recurrence, the soft-capped gates and the output stage (unit norm per head, learned scale,
 // sigmoid gate) are in csrc/mlstm.cu; here: one stacked projection (q | k | v | g | input gate | forget gate) with a
 // float32 result, the recurrence, the output projection.
+#include <algorithm>
+
 #include "args.h"
 #include "linear.h"
 
@@ -43,6 +45,33 @@ public:
         CacheNeed n;                                          // kind None: no keys, no values
         n.state_floats = H_ * (D_ * V_ + D_ + 1);
         return n;
+    }
+
+    // Few tokens (decode steps) in bfloat16: the weight-streaming products, the layer's norm taken into the stacked projection
+    // and the residual sum into the output projection.
+    bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
+        const float* nw;
+        float eps;
+        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
+        if (proj_.weight.dtype != DType::BF16 || out_.weight.dtype != DType::BF16) return false;
+        const long long most = std::max(proj_.weight.rows() * proj_.weight.cols(), out_.weight.rows() * out_.weight.cols());
+        if (ctx.T_cap > std::min(ops::skinny_max_rows(2 * most), ops::SKINNY_NORM_ROWS)) return false;
+        return hidden_ % 32 == 0 && (H_ * V_) % 32 == 0 && proj_.weight.rows() % 8 == 0;
+    }
+
+    void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
+        const float* nw = nullptr;
+        float eps = 0.f;
+        norm.as_rms(&nw, &eps);
+        const int cols = static_cast<int>(proj_.weight.rows());
+        float* proj = static_cast<float*>(ctx.take_tokens(cols, DType::F32));
+        ops::skinny_linear(h, nw, eps, proj_.weight, ctx.T, proj, cols, true, nullptr, ctx.err, ctx.stream);
+        void* y = ctx.take_tokens(static_cast<long long>(H_) * V_, DType::BF16);
+        ops::mlstm_scan(proj, cols, static_cast<const float*>(bias_i_.ptr), static_cast<const float*>(bias_f_.ptr), static_cast<const float*>(norm_.ptr),
+                        ctx, y, H_, D_, V_, cap_, eps_);
+        ctx.give(proj);
+        ops::skinny_linear(y, nullptr, 0.f, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
+        ctx.give(y);
     }
 
     void forward(StepContext& ctx, const void* x, void* out) override {
