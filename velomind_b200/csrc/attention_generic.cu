@@ -100,6 +100,7 @@ static int launch_generic(const void* q, int q_row_stride, const void* kpages, c
         break;
     switch (epl) {
         VM_ATT_CASE(1) VM_ATT_CASE(2) VM_ATT_CASE(3) VM_ATT_CASE(4) VM_ATT_CASE(5) VM_ATT_CASE(6) VM_ATT_CASE(7) VM_ATT_CASE(8)
+        VM_ATT_CASE(9) VM_ATT_CASE(10) VM_ATT_CASE(11) VM_ATT_CASE(12) VM_ATT_CASE(13) VM_ATT_CASE(14) VM_ATT_CASE(15) VM_ATT_CASE(16)
         default: return VM_ERR_UNSUPPORTED;
     }
 #undef VM_ATT_CASE
@@ -112,7 +113,7 @@ VM_API int vm_attention_generic(const void* q, int q_row_stride, const void* kpa
                                 void* out, int n_tokens, int H, int Hkv, int D, float scale, int window, int n_pages,
                                 int act_dtype, int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || D > 256) return VM_ERR_UNSUPPORTED;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || D > 512) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32)
         return launch_generic<float>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, seq_of_token, out,
                                      n_tokens, H, Hkv, D, scale, window, n_pages, err, stream);

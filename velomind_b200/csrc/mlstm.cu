@@ -153,9 +153,9 @@ inline ChunkSizes chunk_sizes(int D, int V) {
     c.VSp = (c.VS + 3) / 4 * 4;
     c.L = 64;
     auto floats = [&](int L) {
-        // Qt [Dp, L], Kt [Dp, L] (finish: S' [Dp, VSp] in its place), Vs [L, VSp], Pt [L, L], 6 float rows of L, 3 double rows of L
-        const size_t second = (size_t)c.Dp * L > (size_t)c.Dp * c.VSp ? (size_t)c.Dp * L : (size_t)c.Dp * c.VSp;
-        return (size_t)c.Dp * L + second + (size_t)L * c.VSp + (size_t)L * L + c.Dp + 6 * (size_t)L + 6 * (size_t)L;
+        // Qt [Dp, L + 8], Kt [Dp, L + 8] (finish: S' [Dp, VSp] in its place), Vs [L, VSp], Pt [L, L], 6 float rows of L, 3 double rows of L
+        const size_t second = (size_t)c.Dp * (L + 8) > (size_t)c.Dp * c.VSp ? (size_t)c.Dp * (L + 8) : (size_t)c.Dp * c.VSp;
+        return (size_t)c.Dp * (L + 8) + second + (size_t)L * c.VSp + (size_t)L * L + c.Dp + 6 * (size_t)L + 6 * (size_t)L;
     };
     while (c.L > 8 && floats(c.L) * sizeof(float) + 64 > 200 * 1024) c.L /= 2;
     c.smem = floats(c.L) * sizeof(float) + 64;
@@ -212,9 +212,9 @@ struct ChunkSmem {
 };
 __device__ __forceinline__ ChunkSmem carve(float* sm, int L, int Dp, int VSp) {
     ChunkSmem m;
-    const size_t second = (size_t)Dp * L > (size_t)Dp * VSp ? (size_t)Dp * L : (size_t)Dp * VSp;
+    const size_t second = (size_t)Dp * (L + 8) > (size_t)Dp * VSp ? (size_t)Dp * (L + 8) : (size_t)Dp * VSp;
     m.Qt = sm;
-    m.Kt = m.Qt + (size_t)Dp * L;
+    m.Kt = m.Qt + (size_t)Dp * (L + 8);
     m.Vs = m.Kt + second;
     m.Pt = m.Vs + (size_t)L * VSp;
     m.nprev = m.Pt + (size_t)L * L;
@@ -243,16 +243,18 @@ mlstm_chunk_local_kernel(const float* __restrict__ proj, int ld, const float* __
     const int v0 = slice * VS, vs = min(VS, V - v0);
     const int off_k = H * D, off_v = 2 * H * D, off_i = 2 * H * D + 2 * H * V, off_f = off_i + H;
     const float q_scale = rsqrtf((float)D);
+    // q and k transposed into rows of L + 8 floats: a warp takes 4 values of d for 8 tokens, which lands in 32 different banks
+    const int LS = L + 8;
     for (int i = tid; i < L * Dp; i += CHUNK_THREADS) {
-        const int j = i / Dp, d = i - j * Dp;
+        const int tile = i >> 5, dt = tile % (Dp / 4), d = 4 * dt + (i & 3), j = 8 * (tile / (Dp / 4)) + ((i & 31) >> 2);
         float q = 0.f, k = 0.f;
         if (j < Lc && d < D) {
             const float* row = proj + (size_t)(c0 + j) * ld;
             q = row[h * D + d] * q_scale;
             k = row[off_k + h * D + d];
         }
-        m.Qt[d * L + j] = q;
-        m.Kt[d * L + j] = k;
+        m.Qt[d * LS + j] = q;
+        m.Kt[d * LS + j] = k;
     }
     for (int i = tid; i < L * VSp; i += CHUNK_THREADS) {
         const int j = i / VSp, v = i - j * VSp;
@@ -269,8 +271,8 @@ mlstm_chunk_local_kernel(const float* __restrict__ proj, int ld, const float* __
         if (st > jt) continue;
         float acc[4][4] = {};
         for (int d = 0; d < Dp; ++d) {
-            const float4 q4 = *reinterpret_cast<const float4*>(m.Qt + d * L + 4 * jt);
-            const float4 k4 = *reinterpret_cast<const float4*>(m.Kt + d * L + 4 * st);
+            const float4 q4 = *reinterpret_cast<const float4*>(m.Qt + d * LS + 4 * jt);
+            const float4 k4 = *reinterpret_cast<const float4*>(m.Kt + d * LS + 4 * st);
             const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
             for (int a = 0; a < 4; ++a)
@@ -333,7 +335,7 @@ mlstm_chunk_local_kernel(const float* __restrict__ proj, int ld, const float* __
             const float vb[4] = {v4.x * w, v4.y * w, v4.z * w, v4.w * w};
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
-                const float k = m.Kt[(4 * dt + a) * L + ss];
+                const float k = m.Kt[(4 * dt + a) * LS + ss];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(k, vb[b], acc[a][b]);
             }
@@ -347,7 +349,7 @@ mlstm_chunk_local_kernel(const float* __restrict__ proj, int ld, const float* __
     if (slice == 0) {
         for (int d = tid; d < D; d += CHUNK_THREADS) {
             float acc = 0.f;
-            for (int ss = 0; ss < Lc; ++ss) acc = fmaf(wend[ss], m.Kt[d * L + ss], acc);
+            for (int ss = 0; ss < Lc; ++ss) acc = fmaf(wend[ss], m.Kt[d * LS + ss], acc);
             dn[((size_t)z * H + h) * D + d] = acc;
         }
         if (tid == 0) {
@@ -407,9 +409,10 @@ mlstm_chunk_finish_kernel(const float* __restrict__ proj, int ld, const float* _
     const int off_i = 2 * H * D + 2 * H * V, off_f = off_i + H;
     const float q_scale = rsqrtf((float)D);
     const size_t zh = (size_t)z * H + h;
+    const int LS = L + 8;
     for (int i = tid; i < L * Dp; i += CHUNK_THREADS) {
-        const int j = i / Dp, d = i - j * Dp;
-        m.Qt[d * L + j] = (j < Lc && d < D) ? proj[(size_t)(c0 + j) * ld + h * D + d] * q_scale : 0.f;
+        const int tile = i >> 5, dt = tile % (Dp / 4), d = 4 * dt + (i & 3), j = 8 * (tile / (Dp / 4)) + ((i & 31) >> 2);
+        m.Qt[d * LS + j] = (j < Lc && d < D) ? proj[(size_t)(c0 + j) * ld + h * D + d] * q_scale : 0.f;
     }
     float* Ss = m.Kt;                     // [Dp, VSp]: the slice's columns of the state at the chunk's start
     for (int i = tid; i < Dp * VSp; i += CHUNK_THREADS) {
@@ -425,7 +428,7 @@ mlstm_chunk_finish_kernel(const float* __restrict__ proj, int ld, const float* _
         const double g = fmax(m_prev, m.c_s[j]);
         const float wl = expf((float)(m.c_s[j] - g)), wo = expf((float)(m_prev - g));
         float old = 0.f;
-        for (int d = 0; d < D; ++d) old = fmaf(m.nprev[d], m.Qt[d * L + j], old);
+        for (int d = 0; d < D; ++d) old = fmaf(m.nprev[d], m.Qt[d * LS + j], old);
         const float nq = fmaf(wl, nq_buf[(size_t)(c0 + j) * H + h], wo * old);
         w_loc[j] = wl;
         w_old[j] = wo;
@@ -438,7 +441,7 @@ mlstm_chunk_finish_kernel(const float* __restrict__ proj, int ld, const float* _
         if (4 * jt >= Lc) continue;
         float acc[4][4] = {};
         for (int d = 0; d < Dp; ++d) {
-            const float4 q4 = *reinterpret_cast<const float4*>(m.Qt + d * L + 4 * jt);
+            const float4 q4 = *reinterpret_cast<const float4*>(m.Qt + d * LS + 4 * jt);
             const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * VSp + 4 * vt);
             const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, sb[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll

@@ -75,13 +75,13 @@ __device__ __forceinline__ void tile_product(ARow a_row, const __nv_bfloat16* __
     const __nv_bfloat16* a_src[2] = {a_row(lr), a_row(lr + 32)};
     const __nv_bfloat16* b_src[2] = {n0 + lr < N ? B + (size_t)(n0 + lr) * K : nullptr, n0 + lr + 32 < N ? B + (size_t)(n0 + lr + 32) * K : nullptr};
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int k0 = 0; k0 < K; k0 += TK) {
-        uint4 av[2], bv[2];
+    uint4 av[2], bv[2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            av[i] = a_src[i] ? *reinterpret_cast<const uint4*>(a_src[i] + k0 + lp) : zero;
-            bv[i] = b_src[i] ? *reinterpret_cast<const uint4*>(b_src[i] + k0 + lp) : zero;
-        }
+    for (int i = 0; i < 2; ++i) {
+        av[i] = a_src[i] ? *reinterpret_cast<const uint4*>(a_src[i] + lp) : zero;
+        bv[i] = b_src[i] ? *reinterpret_cast<const uint4*>(b_src[i] + lp) : zero;
+    }
+    for (int k0 = 0; k0 < K; k0 += TK) {
         __syncthreads();                   // the previous step's fragments are read
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -89,6 +89,13 @@ __device__ __forceinline__ void tile_product(ARow a_row, const __nv_bfloat16* __
             *reinterpret_cast<uint4*>(&Bs[lr + 32 * i][lp]) = bv[i];
         }
         __syncthreads();
+        if (k0 + TK < K) {                 // the next step's pieces are on their way while this one is multiplied
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                av[i] = a_src[i] ? *reinterpret_cast<const uint4*>(a_src[i] + k0 + TK + lp) : zero;
+                bv[i] = b_src[i] ? *reinterpret_cast<const uint4*>(b_src[i] + k0 + TK + lp) : zero;
+            }
+        }
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {
             unsigned a[2][4], b[4][2];
