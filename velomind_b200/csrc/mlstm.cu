@@ -375,16 +375,25 @@ __global__ void mlstm_chunk_carry_kernel(float* __restrict__ state, const int* _
     const bool is_n = e >= D * V;
     float x = st[e];                                   // S elements, then n, lie in this order
     double m = (double)st[(size_t)D * V + D];
-    for (int c = 0; c < chunks; ++c, ++z) {
-        const size_t zh = (size_t)z * H + h;
-        float* slot = is_n ? dn + zh * D + (e - D * V) : dS + zh * (size_t)D * V + e;
-        const float add = *slot;
-        *slot = x;
-        if (e == 0) chunk_m[zh] = m;
-        const double F = chunk_fc[zh * 2], c_last = chunk_fc[zh * 2 + 1];
-        const double g = fmax(m, c_last);
-        x = expf((float)(m - g)) * x + expf((float)(c_last - g)) * add;
-        m = F + g;
+    // eight chunks at a time: their contributions are fetched together (independent loads), then the state walks through them
+    constexpr int AT_ONCE = 8;
+    const size_t stride = is_n ? (size_t)H * D : (size_t)H * D * V;           // from one chunk's entry to the next chunk's
+    float* base = is_n ? dn + ((size_t)z * H + h) * D + (e - D * V) : dS + ((size_t)z * H + h) * (size_t)D * V + e;
+    for (int c = 0; c < chunks; c += AT_ONCE, z += AT_ONCE, base += AT_ONCE * stride) {
+        float add[AT_ONCE];
+#pragma unroll
+        for (int i = 0; i < AT_ONCE; ++i) add[i] = c + i < chunks ? base[i * stride] : 0.f;
+#pragma unroll
+        for (int i = 0; i < AT_ONCE; ++i) {
+            if (c + i >= chunks) break;
+            const size_t zh = (size_t)(z + i) * H + h;
+            base[i * stride] = x;
+            if (e == 0) chunk_m[zh] = m;
+            const double F = chunk_fc[zh * 2], c_last = chunk_fc[zh * 2 + 1];
+            const double g = fmax(m, c_last);
+            x = expf((float)(m - g)) * x + expf((float)(c_last - g)) * add[i];
+            m = F + g;
+        }
     }
     if (!is_n) st[e] = x;
     else end_nm[((size_t)s * H + h) * (D + 1) + (e - D * V)] = x;
@@ -506,10 +515,19 @@ mlstm_step_kernel(const float* __restrict__ proj, int ld, const float* __restric
     float num = 0.f;
     if (v < V) {
         const float bv = b * row[off_v + h * V + v];
-        for (int d = dg; d < D; d += 4) {
-            const float sv = fmaf(a, st[(size_t)d * V + v], ks[d] * bv);
-            st[(size_t)d * V + v] = sv;
-            num = fmaf(sv, qs[d], num);
+        constexpr int AT_ONCE = 8;                     // the state's values are fetched eight at a time, then moved on and stored
+        for (int d0 = dg; d0 < D; d0 += 4 * AT_ONCE) {
+            float old[AT_ONCE];
+#pragma unroll
+            for (int i = 0; i < AT_ONCE; ++i) old[i] = d0 + 4 * i < D ? st[(size_t)(d0 + 4 * i) * V + v] : 0.f;
+#pragma unroll
+            for (int i = 0; i < AT_ONCE; ++i) {
+                const int d = d0 + 4 * i;
+                if (d >= D) break;
+                const float sv = fmaf(a, old[i], ks[d] * bv);
+                st[(size_t)d * V + v] = sv;
+                num = fmaf(sv, qs[d], num);
+            }
         }
     }
     part[tid] = num;

@@ -98,21 +98,16 @@ __device__ __forceinline__ void tile_product(ARow a_row, const __nv_bfloat16* __
         }
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {
+            // fragments through ldmatrix: four 8 x 8 blocks per instruction.  A: rows r..r+15, the two halves of k; B (stored [n][k],
+            // the "col" operand): two n-blocks of 8, the two halves of k each
             unsigned a[2][4], b[4][2];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = wm + 16 * i + g;
-                a[i][0] = *reinterpret_cast<const unsigned*>(&As[r][kk + 2 * t]);
-                a[i][1] = *reinterpret_cast<const unsigned*>(&As[r + 8][kk + 2 * t]);
-                a[i][2] = *reinterpret_cast<const unsigned*>(&As[r][kk + 2 * t + 8]);
-                a[i][3] = *reinterpret_cast<const unsigned*>(&As[r + 8][kk + 2 * t + 8]);
-            }
+            for (int i = 0; i < 2; ++i)
+                vm_ldmatrix_x4(a[i][0], a[i][1], a[i][2], a[i][3], &As[wm + 16 * i + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int n = wn + 8 * j + g;
-                b[j][0] = *reinterpret_cast<const unsigned*>(&Bs[n][kk + 2 * t]);
-                b[j][1] = *reinterpret_cast<const unsigned*>(&Bs[n][kk + 2 * t + 8]);
-            }
+            for (int jj = 0; jj < 2; ++jj)
+                vm_ldmatrix_x4(b[2 * jj][0], b[2 * jj][1], b[2 * jj + 1][0], b[2 * jj + 1][1],
+                               &Bs[wn + 16 * jj + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
