@@ -134,6 +134,31 @@ def test_each_mechanism_alone(name, toy_plugin, tmp_path):
     run_cuts(engine, requests, plain, cuts, 3e-5)
 
 
+def test_equal_router_logits_go_to_the_lower_index(toy_plugin, tmp_path):
+    """Two experts with the same router row and bias tie at every token; the one with the lower index is chosen, in the
+    few-token kernels and (bfloat16, prompts) in the grouped ones."""
+    import velomind_b200 as vm
+    args = {"hidden": 64, "experts": 5, "top": 2, "ff": 32}
+    cfg = probe_config(64, ff_block("routed_experts", args))
+    w = rounded_to_bf16(random_tensors(vm.weight_table(cfg), np.random.default_rng(41), 0.25))
+    p = "layers.0.feed_forward."
+    w[p + "router"][3] = w[p + "router"][1]
+    w[p + "router.b"][3] = w[p + "router.b"][1]
+    requests = S.make_requests(64, (90, 4), seed=5)
+    chosen = K.route(w["embed.weight"].astype(np.float64), w, p, 2)[0]
+    assert (chosen == 1).any() and ((chosen == 1).sum(axis=1) >= (chosen == 3).sum(axis=1)).all()     # 3 never without 1: the tie is real
+    assert (chosen[:, 1] == 1).any()                  # tokens at which the tie decides the second expert
+    mlp = {"router": {"top": 2}, "shared": None}
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks]
+        plain[rid] = x + K.routed_experts(x, w, p, mlp)
+    for dtype, tol, as_bf16 in (("float32", 3e-5, False), ("bfloat16", 1.5e-2, True)):
+        folder = write_model(str(tmp_path / dtype), cfg, w, as_bf16=as_bf16)
+        engine = vm.Engine(vm.load_model(folder, dtype, "cuda:0"), 64 * 4)
+        run_cuts(engine, requests, plain, {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests, tail=3)}, tol)
+
+
 def test_experts_of_many_tokens_bfloat16(toy_plugin, tmp_path):
     """Prompts group their (token, expert) pairs by expert and multiply on the tensor cores; decode steps stream each token's
     experts.  Both against the plain implementation, on bfloat16-exact inputs and weights, so that the routing is the same."""

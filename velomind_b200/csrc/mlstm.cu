@@ -651,6 +651,12 @@ VM_API int vm_mlstm_step(const float* proj, int ld, const float* bias_i, const f
     return vm_launch_status();
 }
 
+// whether the token-by-token kernel takes heads of these sizes (its block holds a head's whole S in shared memory)
+VM_API int vm_mlstm_scan_fits(int D, int V) {
+    const int widest = D > V ? D : V;
+    return widest <= 1024 && ((size_t)D * V + 4 * D + 8 + 4 * 32) * sizeof(float) <= 200 * 1024 ? 1 : 0;
+}
+
 VM_API int vm_mlstm_scan(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state, const int* cu_tokens,
                          const int* slots, void* out, int B, int H, int D, int V, float cap, float eps, int act_dtype, cudaStream_t stream) {
     if (B <= 0) return 0;

@@ -244,7 +244,17 @@ int launch_experts(const void* x, const void* w_up, const void* w_down, const vo
                    int act_kind_shared, void* act, void* out, cudaStream_t stream) {
     const int rows = top * ff + ff_shared;
     const int warps = 8;
-    if ((size_t)hidden * sizeof(float) > 48 * 1024 || (size_t)rows * sizeof(float) > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    const size_t up_smem = (size_t)hidden * sizeof(float), down_smem = (size_t)rows * sizeof(float);
+    if (up_smem > 200 * 1024 || down_smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
+    static size_t up_raised = 48 * 1024, down_raised = 48 * 1024;       // per instantiation
+    if (up_smem > up_raised) {
+        if (cudaFuncSetAttribute(experts_up_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)up_smem) != cudaSuccess) return vm_launch_status();
+        up_raised = up_smem;
+    }
+    if (down_smem > down_raised) {
+        if (cudaFuncSetAttribute(experts_down_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down_smem) != cudaSuccess) return vm_launch_status();
+        down_raised = down_smem;
+    }
     const int per_block = warps * ROWS_PER_WARP;
     vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, (const T*)x,
                   (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, (T*)act);

@@ -23,14 +23,14 @@ __device__ __forceinline__ float act_of(float z, int kind) {
 }
 
 // one block: counts, padded offsets, placement.  row_of_pair [T * top]; token_of_row [row_cap] (-1: padding); expert_of_tile [row_cap / TM] (-1: unused)
-__global__ void group_pairs_kernel(const int* __restrict__ chosen, int n_pairs, int top, int E, int row_cap, int* __restrict__ row_of_pair,
+__global__ void group_pairs_kernel(const int* __restrict__ chosen, int n_pairs, int top, int E, int row_cap, int tile, int* __restrict__ row_of_pair,
                                    int* __restrict__ token_of_row, int* __restrict__ expert_of_tile) {
     extern __shared__ int sh[];            // [E] counts, [E] cursors
     int* count = sh;
     int* cursor = sh + E;
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     for (int i = threadIdx.x; i < row_cap; i += blockDim.x) token_of_row[i] = -1;
-    for (int i = threadIdx.x; i < row_cap / TM; i += blockDim.x) expert_of_tile[i] = -1;
+    for (int i = threadIdx.x; i < row_cap / tile; i += blockDim.x) expert_of_tile[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
         const int e = chosen[i];
@@ -40,10 +40,10 @@ __global__ void group_pairs_kernel(const int* __restrict__ chosen, int n_pairs, 
     if (threadIdx.x == 0) {
         int at = 0;
         for (int e = 0; e < E; ++e) {
-            const int tiles = (count[e] + TM - 1) / TM;
+            const int tiles = (count[e] + tile - 1) / tile;
             cursor[e] = at;
-            for (int k = 0; k < tiles; ++k) expert_of_tile[at / TM + k] = e;
-            at += tiles * TM;
+            for (int k = 0; k < tiles; ++k) expert_of_tile[at / tile + k] = e;
+            at += tiles * tile;
         }
     }
     __syncthreads();
@@ -171,6 +171,18 @@ __global__ void experts_combine_kernel(const float* __restrict__ y, const int* _
     }
 }
 
+// x_sorted[row] = x[token_of_row[row]], zeros for a row of padding; 16 bytes per thread
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ token_of_row, int rows, int hidden,
+                                   __nv_bfloat16* __restrict__ x_sorted) {
+    const int per_row = hidden / 8;
+    const size_t n = (size_t)rows * per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / per_row), piece = (int)(i - (size_t)row * per_row);
+        const int tok = token_of_row[row];
+        reinterpret_cast<uint4*>(x_sorted)[i] = tok >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)tok * hidden)[piece] : make_uint4(0, 0, 0, 0);
+    }
+}
+
 template <typename T> __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int kind) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = vm_from_float<T>(act_of(vm_to_float(in[i]), kind));
@@ -192,7 +204,7 @@ VM_API int vm_experts_grouped(const void* x, const void* w_up, const void* w_dow
     if (hidden % TK || ff % TK || top <= 0 || E <= 0) return VM_ERR_UNSUPPORTED;
     if (row_cap % TM || row_cap < vm_experts_grouped_rows(T, top, E)) return VM_ERR_BAD_ARG;
     if ((size_t)2 * E * sizeof(int) > 48 * 1024) return VM_ERR_UNSUPPORTED;
-    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, row_of_pair, token_of_row,
+    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, TM, row_of_pair, token_of_row,
                                                                                   expert_of_tile);
     int st = vm_launch_status();
     if (st) return st;
@@ -205,6 +217,44 @@ VM_API int vm_experts_grouped(const void* x, const void* w_up, const void* w_dow
     experts_down_grouped_kernel<<<dim3(tiles, (hidden + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down,
                                                                                         expert_of_tile, hidden, ff, y);
     st = vm_launch_status();
+    if (st) return st;
+    const size_t n = (size_t)T * hidden;
+    const size_t want = (n + 255) / 256;
+    experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, weight, shared_y, shared_gate, T, hidden, top,
+                                                                                         (__nv_bfloat16*)out);
+    return vm_launch_status();
+}
+
+// The same with the experts' products on tcgen05 (csrc/tc_gemm.cu, grouped): runs padded to tiles of 128 rows, the rows gathered
+// into x_sorted [row_cap, hidden] first.  row_cap from vm_experts_grouped_rows_tiled(T, top, E, 128); hidden and ff multiples of 8.
+VM_API long long vm_experts_grouped_rows_tiled(int T, int top, int E, int tile) {
+    return ((long long)T * top + (long long)E * (tile - 1) + tile - 1) / tile * tile;
+}
+
+VM_API int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                                 const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                                 int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, float* y, void* out, int* err,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    constexpr int TILE = 128;
+    if (hidden % 8 || ff % 8 || top <= 0 || E <= 0) return VM_ERR_UNSUPPORTED;
+    if (row_cap % TILE || row_cap < vm_experts_grouped_rows_tiled(T, top, E, TILE)) return VM_ERR_BAD_ARG;
+    if ((size_t)2 * E * sizeof(int) > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, TILE, row_of_pair, token_of_row,
+                                                                                  expert_of_tile);
+    int st = vm_launch_status();
+    if (st) return st;
+    const int rows = (int)vm_experts_grouped_rows_tiled(T, top, E, TILE);      // rows this step can need at most (the capacity may be larger)
+    {
+        const size_t n = (size_t)rows * (hidden / 8), want = (n + 255) / 256;
+        gather_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)x, token_of_row, rows, hidden,
+                                                                                         (__nv_bfloat16*)x_sorted);
+        st = vm_launch_status();
+        if (st) return st;
+    }
+    st = vm_tc_grouped_linear(x_sorted, hidden, w_up, rows, ff, hidden, E, expert_of_tile, act, ff, 0, act_kind, err, stream);
+    if (st) return st;
+    st = vm_tc_grouped_linear(act, ff, w_down, rows, hidden, ff, E, expert_of_tile, y, hidden, 1, -1, err, stream);
     if (st) return st;
     const size_t n = (size_t)T * hidden;
     const size_t want = (n + 255) / 256;

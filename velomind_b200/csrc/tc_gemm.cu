@@ -43,7 +43,17 @@ struct TcParams {
     int* err;                        // cache faults (2) and abandoned waits (4)
     int tiles_m, tiles_n;
     int tma_residual;                // the residual sum leaves through TMA reduce-add (map_h is valid)
+    // grouped products: row tile m multiplies with the rows [group * group_rows, +N) of a stacked W, group = tile_group[m]
+    // (-1: the tile is not used and every role skips it); null: one W for all rows
+    const int* tile_group; int group_rows, stacked_rows;
+    int act_plus_one;                // store epilogues: an activation (VM_ACT_* + 1) applied before the store; 0: none
 };
+
+__device__ __forceinline__ float tc_activate(float z, int kind) {
+    if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -152,6 +162,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int m0 = tile_m * TC_BM;
                 int n0 = tile_n * BN, n1 = -1;           // where the tile's W rows start (two ranges for swiglu)
                 if (p.epi == TC_SWIGLU) { n0 = tile_n * half; n1 = p.I + n0; }
+                if (p.tile_group) {
+                    const int group = p.tile_group[tile_m];
+                    if (group < 0) continue;             // (the other roles skip the same tiles)
+                    n0 += group * p.group_rows;
+                }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = (uint32_t)(it / STAGES);
@@ -184,7 +199,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             int it = 0, t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (p.tile_group && p.tile_group[tile / p.tiles_n] < 0) continue;           // t counts the tiles that are multiplied
                 const int a = t & 1;
                 ok = mbar_wait(acce0 + 8 * a, (((uint32_t)t >> 1) & 1u) ^ 1u, abort_p);     // the epilogue has drained this accumulator
                 if (!ok) break;
@@ -207,14 +223,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_commit(empty0 + 8 * s);            // the stage is free once these MMAs have read it
                 }
                 if (ok) tc_commit(accf0 + 8 * a);         // the accumulator is complete once all MMAs are done
+                ++t;
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue: warps 2..5, lanes 32 * (warp % 4) ..
         const int quarter = warp & 3;
         int t = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int tile_m = tile / p.tiles_n, tile_n = tile - tile_m * p.tiles_n;
+        if (p.tile_group && p.tile_group[tile_m] < 0) continue;
         const int m0 = tile_m * TC_BM;
         int n0 = tile_n * BN;
         if (p.epi == TC_SWIGLU) n0 = tile_n * half;
@@ -258,6 +276,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         continue;
                     }
                     if (!row_ok || col0 >= p.N) continue;
+                    if (p.act_plus_one) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(tc_activate(__uint_as_float(v[j]), p.act_plus_one - 1));
+                    }
                     if (p.epi == TC_STORE_BF16) {
                         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + col0;
                         if (col0 + 32 <= p.N && (p.out_stride & 7) == 0) {
@@ -363,6 +385,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * acc) : "memory");
+        ++t;
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // this lane's reduce-adds have landed
     }
@@ -413,7 +436,7 @@ int tc_launch(const void* A, long long lda, const void* W, TcParams p, int tiles
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, p.M, p.K, lda, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mb, W, p.epi == TC_SWIGLU ? 2 * p.I : p.N, p.K, p.K, b_box_rows);
+    rc = make_map(&mb, W, p.tile_group ? p.stacked_rows : (p.epi == TC_SWIGLU ? 2 * p.I : p.N), p.K, p.K, b_box_rows);
     if (rc) return rc;
     CUtensorMap mh = ma;                                   // a placeholder unless the residual leaves through TMA
     p.tma_residual = 0;
@@ -464,6 +487,23 @@ VM_API int vm_tc_linear(const void* A, long long lda, const void* W, int M, int 
     p.M = M; p.N = N; p.K = K; p.out = out; p.out_stride = out_stride; p.h = residual_h; p.err = err;
     p.epi = residual_h ? TC_RESIDUAL : (out_f32 ? TC_STORE_F32 : TC_STORE_BF16);
     // narrow tiles when wide ones would leave most SMs idle
+    const long long tiles128 = (long long)((N + 127) / 128) * ((M + TC_BM - 1) / TC_BM);
+    if (tiles128 >= 148) return tc_launch<128>(A, lda, W, p, (N + 127) / 128, 128, stream);
+    return tc_launch<64>(A, lda, W, p, (N + 63) / 64, 64, stream);
+}
+
+// Grouped: the rows of A come in tiles of 128 that each belong to one group (tile_group[tile], -1: unused); tile t multiplies
+// with W[group * N .. group * N + N) of the stacked W [groups * N, K].  out [M, out_stride] bf16 (an activation VM_ACT_*
+// applied first; act_kind -1: none) or float32.
+VM_API int vm_tc_grouped_linear(const void* A, long long lda, const void* W, int M, int N, int K, int groups, const int* tile_group,
+                                void* out, int out_stride, int out_f32, int act_kind, int* err, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (K % 8 != 0 || N <= 0 || groups <= 0 || tile_group == nullptr) return VM_ERR_UNSUPPORTED;
+    TcParams p{};
+    p.M = M; p.N = N; p.K = K; p.out = out; p.out_stride = out_stride; p.err = err;
+    p.epi = out_f32 ? TC_STORE_F32 : TC_STORE_BF16;
+    p.tile_group = tile_group; p.group_rows = N; p.stacked_rows = groups * N;
+    p.act_plus_one = act_kind >= 0 ? act_kind + 1 : 0;
     const long long tiles128 = (long long)((N + 127) / 128) * ((M + TC_BM - 1) / TC_BM);
     if (tiles128 >= 148) return tc_launch<128>(A, lda, W, p, (N + 127) / 128, 128, stream);
     return tc_launch<64>(A, lda, W, p, (N + 63) / 64, 64, stream);

@@ -117,7 +117,7 @@ inline void mlstm_scan(const float* proj, int ld, const float* bias_i, const flo
         c.give(scratch);
         return;
     }
-    if (ctx.T_cap <= MLSTM_SCAN_MAX_TOKENS) {
+    if (ctx.T_cap <= MLSTM_SCAN_MAX_TOKENS && vm_mlstm_scan_fits(D, V)) {
         check(vm_mlstm_scan(proj, ld, bias_i, bias_f, norm_w, ctx.state(), ctx.cu_tokens, ctx.slots, out, ctx.B, H, D, V, cap, eps, code(ctx.act_dtype),
                             ctx.stream),
               "mlstm_scan", ctx.stream);
@@ -160,6 +160,17 @@ inline void experts_grouped(const void* x, const DeviceTensor& up, const DeviceT
                              token_of_row, expert_of_tile, act, y, out, s),
           "experts_grouped", s);
     counters().own_launches += 3;       // four kernels
+}
+
+inline void experts_grouped_tc(const void* x, const DeviceTensor& up, const DeviceTensor& down, const int* chosen, const float* weight,
+                               const float* shared_y, const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap,
+                               int* row_of_pair, int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, float* y, void* out, int* err,
+                               cudaStream_t s) {
+    Timed t("experts_grouped_tc", s);
+    check(vm_experts_grouped_tc(x, up.ptr, down.ptr, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, E, act_kind, row_cap, row_of_pair,
+                                token_of_row, expert_of_tile, x_sorted, act, y, out, err, s),
+          "experts_grouped_tc", s);
+    counters().own_launches += 4;       // five kernels
 }
 
 // out = x W^T.  x [T, K] (row stride ldx), W [N, K], out [T, N]; a library matrix product, as in the reference

@@ -53,6 +53,7 @@ int vm_mlstm_scan(const float* proj, int ld, const float* bias_i, const float* b
                   const int* cu_tokens, const int* slots, void* out, int B, int H, int D, int V, float cap, float eps, int act_dtype,
                   cudaStream_t stream);
 
+int vm_mlstm_scan_fits(int D, int V);      // 1 if vm_mlstm_scan takes heads of these sizes
 // the same recurrence chunk by chunk (prompts): scratch of vm_mlstm_chunk_scratch_floats(T, B, H, D, V) floats
 long long vm_mlstm_chunk_scratch_floats(int T, int B, int H, int D, int V);
 int vm_mlstm_chunks(const float* proj, int ld, const float* bias_i, const float* bias_f, const float* norm_w, float* state,
@@ -102,6 +103,12 @@ int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, cons
                        const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
                        int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream);
 int vm_activation(const void* in, void* out, long long n, int kind, int act_dtype, cudaStream_t stream);
+// the same with the experts' products on tcgen05: runs padded to tiles of 128 rows, x_sorted bf16 [row_cap, hidden] as one more scratch
+long long vm_experts_grouped_rows_tiled(int T, int top, int E, int tile);
+int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                          const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                          int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, float* y, void* out, int* err,
+                          cudaStream_t stream);
 
 // ---- skinny_gemm.cu: weight-streaming products for few rows (bfloat16 weights [N, K])
 // (err: the step's error word, may be null; the kernel for large weight matrices reports a wait that ran out there)
@@ -119,6 +126,9 @@ int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float eps, c
 int vm_tc_linear(const void* A, long long lda, const void* W, int M, int N, int K, void* out, int out_stride, int out_f32,
                  float* residual_h, int* err, cudaStream_t stream);
 int vm_tc_swiglu(const void* A, long long lda, const void* W, int M, int I, int K, void* out, int* err, cudaStream_t stream);
+// grouped: row tile t of A (128 rows) multiplies with rows [g * N, g * N + N) of the stacked W [groups * N, K], g = tile_group[t] (-1: unused)
+int vm_tc_grouped_linear(const void* A, long long lda, const void* W, int M, int N, int K, int groups, const int* tile_group,
+                         void* out, int out_stride, int out_f32, int act_kind, int* err, cudaStream_t stream);
 int vm_tc_qkv_rope(const void* A, long long lda, const void* W, int M, int K, void* q_out, const int* positions,
                    const int* seq_of_token, const int* block_table, int max_blocks, const float* inv_freq, int rot_dim,
                    int pairing, void* kpages, void* vpages, int H, int Hkv, int D, int n_pages, int* err, cudaStream_t stream);

@@ -87,14 +87,23 @@ public:
                 ops::linear(u, DType::BF16, sff_, s_down_, shared_y, DType::F32, ctx.T, ctx.stream);
                 ctx.give(u);
             }
-            const int row_cap = static_cast<int>(vm_experts_grouped_rows(ctx.T_cap, top_, E_));
+            // the experts' tiles on tcgen05 from TC_FROM_TOKENS on (tiles of 128 rows, rows gathered first), on mma.sync below
+            const bool tc = ctx.T_cap >= TC_FROM_TOKENS && ctx.err != nullptr;
+            const int row_cap = static_cast<int>(tc ? vm_experts_grouped_rows_tiled(ctx.T_cap, top_, E_, 128) : vm_experts_grouped_rows(ctx.T_cap, top_, E_));
             int* row_of_pair = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
             int* token_of_row = static_cast<int*>(ctx.take(row_cap, DType::I32));
             int* expert_of_tile = static_cast<int*>(ctx.take(row_cap / 64, DType::I32));
             void* act = ctx.take(static_cast<long long>(row_cap) * ff_, DType::BF16);
             float* y = static_cast<float*>(ctx.take(static_cast<long long>(row_cap) * hidden_, DType::F32));
-            ops::experts_grouped(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, E_, act_, row_cap, row_of_pair, token_of_row,
-                                 expert_of_tile, act, y, out, ctx.stream);
+            if (tc) {
+                void* x_sorted = ctx.take(static_cast<long long>(row_cap) * hidden_, DType::BF16);
+                ops::experts_grouped_tc(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, E_, act_, row_cap, row_of_pair,
+                                        token_of_row, expert_of_tile, x_sorted, act, y, out, ctx.err, ctx.stream);
+                ctx.give(x_sorted);
+            } else {
+                ops::experts_grouped(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, E_, act_, row_cap, row_of_pair,
+                                     token_of_row, expert_of_tile, act, y, out, ctx.stream);
+            }
             ctx.give(y);
             ctx.give(act);
             ctx.give(expert_of_tile);
@@ -116,6 +125,7 @@ public:
     }
 
     static constexpr int GROUPED_FROM_TOKENS = 64;      // a step's capacity above which the pairs are grouped by expert
+    static constexpr int TC_FROM_TOKENS = 256;          // ... and from which the experts' tiles run on tcgen05
 
 private:
     int hidden_, E_, top_, ff_, act_, sff_, sact_;
