@@ -297,7 +297,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     } else if (p.epi == TC_STORE_F32) {
                         float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride + col0;
-                        for (int j = 0; j < 32 && col0 + j < p.N; ++j) o[j] = __uint_as_float(v[j]);
+                        if (col0 + 32 <= p.N && (p.out_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)       // a lane's 128 bytes of its row in eight 16-byte stores
+                                *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                                                                __uint_as_float(v[j + 3]));
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j) o[j] = __uint_as_float(v[j]);
+                        }
                     } else {
                         float* o = p.h + (size_t)row * p.N + col0;
                         if (col0 + 32 <= p.N && (p.N & 3) == 0) {
