@@ -553,6 +553,28 @@ def test_skinny_swiglu(M, I, K, skinny_kernel):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("act", [1, 2])
+@pytest.mark.parametrize("M,I,K", [(1, 64, 96), (8, 320, 256), (32, 2816, 1024)])      # (the last one streams its weights through the ring)
+def test_skinny_gated_with_another_activation(M, I, K, act):
+    """The gated epilogue with the tanh form of GELU (1) and squared ReLU (2) as the gate's activation."""
+    o = ops()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    hres = torch.randn(M, K, generator=_gen(M + act)) * 2
+    nw = 1 + 0.1 * torch.randn(K, generator=_gen(I))
+    w = _bf(torch.randn(2 * I, K, generator=_gen(K)) * 0.2)
+    xn = _rms_ref(hres, nw, 1e-6)
+    gu = xn.float() @ w.float().t()
+    g, u = gu[:, :I], gu[:, I:]
+    gate = 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) if act == 1 else torch.clamp(g, min=0) ** 2
+    want = gate * u
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.skinny_gated(hres.to(DEV), (nw.to(DEV), 1e-6), w.to(DEV), out, act, err=err)
+    assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
+    o.skinny_gated(xn.to(DEV), None, w.to(DEV), out, act, err=err)
+    assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("H,Hkv,D,K,rot", [(4, 2, 16, 64, 16), (3, 1, 32, 96, 32), (9, 3, 64, 576, 64), (5, 5, 48, 160, 0), (2, 1, 128, 256, 128),
                                            (40, 8, 64, 96, 64), (32, 32, 64, 2048, 64)])   # (the last two: CTAs take several column tiles)
 def test_skinny_qkv_rope(H, Hkv, D, K, rot, skinny_kernel):

@@ -93,6 +93,10 @@ MECHANISMS = {
     "latent_attention_odd": ("mixer", "latent_attention", {"hidden": 56, "heads": 2, "dim": 10, "vdim": 14, "q_rank": 20, "kv_rank": 36, "scale": 0.5, "eps": 1e-6}),
     "mlstm": ("mixer", "mlstm", {"hidden": 72, "heads": 3, "dim": 12, "vdim": 20, "gate_cap": 9.0, "eps": 1e-5}),
     "mlstm_wide": ("mixer", "mlstm", {"hidden": 64, "heads": 1, "dim": 72, "vdim": 40, "gate_cap": 30.0, "eps": 1e-6}),
+    # a key size that is no multiple of four and values wider than one block's 64 columns (two slices, the second one ragged)
+    "mlstm_sliced": ("mixer", "mlstm", {"hidden": 64, "heads": 2, "dim": 18, "vdim": 80, "gate_cap": 12.0, "eps": 1e-5}),
+    # a latent of 64 values: long prompts take the tcgen05 attention kernels, all query heads on the one latent "head"
+    "latent_attention_64": ("mixer", "latent_attention", {"hidden": 64, "heads": 4, "dim": 16, "vdim": 32, "q_rank": 32, "kv_rank": 64, "scale": 0.3, "eps": 1e-6}),
     "gated_gelu": ("feed_forward", "gated", {"hidden": 64, "intermediate": 88, "activation": "gelu_tanh", "gate": "gate", "up": "up", "down": "down"}),
     "experts_shared": ("feed_forward", "routed_experts", {"hidden": 64, "experts": 6, "top": 2, "ff": 24, "shared_ff": 40}),
     "experts_top_one": ("feed_forward", "routed_experts", {"hidden": 48, "experts": 7, "top": 1, "ff": 16}),
@@ -112,15 +116,18 @@ def plain_mechanism(name, args, x, w):
     return K.routed_experts(x, w, "layers.0.feed_forward.", mlp)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(MECHANISMS))
-def test_each_mechanism_alone(name, toy_plugin, tmp_path):
+def test_each_mechanism_alone(name, dtype, toy_plugin, tmp_path):
     import velomind_b200 as vm
     role, kind, args = MECHANISMS[name]
     cfg = probe_config(args["hidden"], mixer_block(kind, args) if role == "mixer" else ff_block(kind, args))
     rng = np.random.default_rng(sum(name.encode()))
     w = random_tensors(vm.weight_table(cfg), rng, 0.25)
-    folder = write_model(str(tmp_path / name), cfg, w)
-    engine = vm.Engine(vm.load_model(folder, "float32", "cuda:0"), 64 * 6, max_slots=3)
+    if dtype == "bfloat16":
+        w = rounded_to_bf16(w)              # stored as bfloat16; the plain implementation runs on the same rounded numbers
+    folder = write_model(str(tmp_path / name), cfg, w, as_bf16=dtype == "bfloat16")
+    engine = vm.Engine(vm.load_model(folder, dtype, "cuda:0"), 64 * 6, max_slots=3)
     requests = S.make_requests(args["hidden"], (70, 5, 130, 64, 1, 65), seed=3)
     plain = {}
     for rid, toks in requests.items():
@@ -131,7 +138,27 @@ def test_each_mechanism_alone(name, toy_plugin, tmp_path):
         assert len(set(K.route(x, w, "layers.0.feed_forward.", args["top"])[0].reshape(-1).tolist())) == args["experts"]
     cuts = standard_cuts(requests)
     cuts["pieces"] = steps_in_pieces(requests, (2, 3, 64, 1, 65))
-    run_cuts(engine, requests, plain, cuts, 3e-5)
+    run_cuts(engine, requests, plain, cuts, 3e-5 if dtype == "float32" else 2e-2)
+
+
+def test_a_long_prompt_over_a_latent_of_64_values(toy_plugin, tmp_path):
+    """1,500 tokens: the block table is wide enough for the tcgen05 prefill attention kernels, which then serve four query
+    heads on one shared latent that is key and value at once; then decode steps over the same pages."""
+    import velomind_b200 as vm
+    role, kind, args = MECHANISMS["latent_attention_64"]
+    cfg = probe_config(64, mixer_block(kind, args))
+    w = rounded_to_bf16(random_tensors(vm.weight_table(cfg), np.random.default_rng(77), 0.25))
+    folder = write_model(str(tmp_path / "long"), cfg, w, as_bf16=True)
+    engine = vm.Engine(vm.load_model(folder, "bfloat16", "cuda:0"), 64 * 40, max_slots=2)
+    requests = S.make_requests(64, (1500, 2100), seed=6)
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks]
+        plain[rid] = x + K.latent_attention(x, w, "layers.0.mixer.", args, args["eps"])
+    sparse = lambda n: sorted(set(range(0, n, 97)) | {n - 1})
+    whole = [{"step": i, "entries": [{"id": rid, "tokens": toks, "want": sparse(len(toks))}], "end": [rid]} for i, (rid, toks) in enumerate(requests.items())]
+    run_cuts(engine, requests, plain, {"whole": whole, "tail": S.steps_tail_one_by_one({"r0": requests["r0"]}, tail=6)}, 2e-2)
+    assert engine.counters["tc_attention_calls"] >= 3           # the prompts of all three steps took a tcgen05 kernel
 
 
 def test_equal_router_logits_go_to_the_lower_index(toy_plugin, tmp_path):

@@ -22,6 +22,7 @@ struct SkinnyParams {
     int out_stride;
     float* h;                    // residual [M, N]
     int I;                       // swiglu: rows of Wg (and of Wu)
+    int gate_act;                // swiglu: the activation of the gate (VM_ACT_SILU = 0, VM_ACT_GELU_TANH, VM_ACT_RELU_SQUARED)
     // rope_kv
     const int* positions; const int* seq_of_token; const int* block_table; int max_blocks;
     const float* inv_freq; int rot_dim;
@@ -35,6 +36,13 @@ struct SkinnyParams {
 // `item` is the work item (what item_index is for the stand-alone kernel); `smem` the CTA's dynamic shared memory.
 // PDL: launched with programmatic dependent launch (weights may be fetched before the predecessor has finished).
 // The output columns of a work item: tile A's first column, tile B's, and (rope_kv) the head they lie in.
+// the gate's activation of the gated epilogue, float32
+__device__ __forceinline__ float skinny_gate(float z, int kind) {
+    if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+    return z * (1.0f / (1.0f + expf(-z)));
+}
+
 struct SkinnyCols { int nA, nB, head; };
 __device__ __forceinline__ SkinnyCols skinny_cols(const SkinnyParams& p, int item_index) {
     SkinnyCols c{0, 0, 0};
@@ -268,8 +276,7 @@ __device__ __forceinline__ void skinny_run(const SkinnyParams& p, const int firs
                 if (two) o[nB + c] = res_b[it] + vB;
             } break;
             case EPI_SWIGLU: {
-                const float sig = 1.0f / (1.0f + expf(-vA));
-                static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
+                static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn(skinny_gate(vA, p.gate_act) * vB);
             } break;
             case EPI_ROPE_KV: {
                 const int pos = row_pos[it];

@@ -178,15 +178,21 @@ VM_API int vm_skinny_linear(const void* A, int pro, const float* norm_w, float e
     return skinny_dispatch(p, items, stream);
 }
 
-// out[M, I] = silu(x Wg^T) * (x Wu^T) with x = A (pro 0) or rmsnorm(h) (pro 1); W = [Wg; Wu] is [2I, K].
-VM_API int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K,
-                            void* out, int* err, cudaStream_t stream) {
-    if (I % 8 != 0) return VM_ERR_UNSUPPORTED;
+// out[M, I] = act(x Wg^T) * (x Wu^T) with x = A (pro 0) or rmsnorm(h) (pro 1); W = [Wg; Wu] is [2I, K]; act is VM_ACT_*.
+VM_API int vm_skinny_gated(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, int act,
+                           void* out, int* err, cudaStream_t stream) {
+    if (I % 8 != 0 || act < VM_ACT_SILU || act > VM_ACT_RELU_SQUARED) return VM_ERR_UNSUPPORTED;
     SkinnyParams p{};
     p.err = err;
     p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = 2 * I; p.K = K;
-    p.out = out; p.out_stride = I; p.I = I; p.epi = EPI_SWIGLU; p.tiles = 2;
+    p.out = out; p.out_stride = I; p.I = I; p.epi = EPI_SWIGLU; p.tiles = 2; p.gate_act = act;
     return skinny_dispatch(p, I / 8, stream);
+}
+
+// the same with act = SiLU
+VM_API int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K,
+                            void* out, int* err, cudaStream_t stream) {
+    return vm_skinny_gated(A, pro, norm_w, eps, W, M, I, K, VM_ACT_SILU, out, err, stream);
 }
 
 // q_out[M, H*D] = rope(x Wq^T); rope(x Wk^T) and x Wv^T go to the cache pages; W = [Wq; Wk; Wv] is [(H+2Hkv)*D, K].

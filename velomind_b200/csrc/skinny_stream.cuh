@@ -297,8 +297,7 @@ skinny_stream_kernel(const SkinnyParams p) {
                         if (two) o[nB + c] = res_b + vB;
                     } break;
                     case EPI_SWIGLU: {
-                        const float sig = 1.0f / (1.0f + expf(-vA));
-                        static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
+                        static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn(skinny_gate(vA, p.gate_act) * vB);
                     } break;
                     case EPI_ROPE_KV: {
                         float ya = vA, yb = vB;

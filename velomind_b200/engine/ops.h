@@ -214,6 +214,12 @@ inline void skinny_swiglu(const void* x, const float* norm_w, float eps, const D
     check(vm_skinny_swiglu(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, I, static_cast<int>(W.cols()), out, err, s), "skinny_swiglu", s);
 }
 
+inline void skinny_gated(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, int I, int act, void* out, int* err,
+                         cudaStream_t s) {
+    Timed t("skinny_gated", s);
+    check(vm_skinny_gated(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, I, static_cast<int>(W.cols()), act, out, err, s), "skinny_gated", s);
+}
+
 inline void skinny_qkv_rope(const void* x, const float* norm_w, float eps, const DeviceTensor& W, void* q_out, const StepContext& ctx, const KVView& kv,
                             const RotaryTable& rot, int H, int Hkv, int D) {
     Timed t("skinny_qkv_rope", ctx.stream);

@@ -116,6 +116,8 @@ int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, con
                      int out_stride, int out_f32, float* residual_h, int* err, cudaStream_t stream);
 int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, void* out,
                      int* err, cudaStream_t stream);
+int vm_skinny_gated(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, int act, void* out,
+                    int* err, cudaStream_t stream);      // vm_skinny_swiglu with the gate's activation (VM_ACT_*) as an argument
 void vm_skinny_variant(int variant);       // 0 choose by size, 1 / 2 force one of the two kernels (tests, measurements)
 int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int K, void* q_out,
                        const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,

@@ -313,6 +313,14 @@ def skinny_swiglu(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor
                                       _c_int(out.shape[1]), _c_int(K), _ptr(_contig(out, "out")), _ptr(err), _stream()), "skinny_swiglu")
 
 
+def skinny_gated(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor, act: int, err: Optional[torch.Tensor] = None) -> None:
+    """out[M, I] = act(x' Wg^T) * (x' Wu^T) with act 0 SiLU, 1 the tanh form of GELU, 2 squared ReLU; otherwise as skinny_swiglu."""
+    M, K = x.shape
+    pro, nw, eps = _norm_args(norm)
+    _check(library().vm_skinny_gated(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M), _c_int(out.shape[1]),
+                                     _c_int(K), _c_int(act), _ptr(_contig(out, "out")), _ptr(err), _stream()), "skinny_gated")
+
+
 def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
                     seq_of_token: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int,
                     k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int,

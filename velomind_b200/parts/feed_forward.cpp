@@ -7,8 +7,8 @@ namespace vmb {
 // down(silu(gate(x)) * up(x)), no biases (examples/common/llama/llama_graph.cpp:22-28,122-138).  gate and up are one
 // stacked product; the activation kernel reads both halves.
 //
-// `activation` (VM_ACT_*) and the three tensors' names are arguments; the fused kernels know SiLU, any other activation runs
-// as product, activation kernel, product.
+// `activation` (VM_ACT_*) and the three tensors' names are arguments; the weight-streaming kernels take the activation as an
+// argument, the tcgen05 epilogue knows SiLU (other activations take the library products there).
 class SwiGLU : public FeedForward {
 public:
     SwiGLU(int hidden, int intermediate, int activation = VM_ACT_SILU, std::string gate = "gate_proj.weight", std::string up = "up_proj.weight",
@@ -38,7 +38,6 @@ public:
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
-        if (act_ != VM_ACT_SILU) return false;
         if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
         if (gate_up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
         if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && I_ % 32 == 0;
@@ -51,7 +50,7 @@ public:
         float eps = 0.f;
         norm.as_rms(&nw, &eps);
         const bool skinny = ctx.T_cap <= max_rows();
-        const bool tc = !skinny && ops::tc_fused_rows(ctx) && I_ % 64 == 0;
+        const bool tc = !skinny && act_ == VM_ACT_SILU && ops::tc_fused_rows(ctx) && I_ % 64 == 0;      // (that epilogue knows SiLU)
         if (!skinny && !tc) {
             // the library's products: norm, gate and up, SwiGLU, down added into h by the product itself
             void* x = ctx.take_tokens(hidden_, DType::BF16);
@@ -60,7 +59,7 @@ public:
             ops::linear(x, DType::BF16, hidden_, gate_up_.weight, gu, DType::BF16, ctx.T, ctx.stream);
             ctx.give(x);
             void* a = ctx.take_tokens(I_, DType::BF16);
-            ops::swiglu(gu, a, ctx.T, I_, DType::BF16, ctx.stream);
+            ops::gated_activation(gu, a, ctx.T, I_, act_, DType::BF16, ctx.stream);
             ctx.give(gu);
             ops::linear_residual(a, I_, down_.weight, h, ctx.T, ctx.stream);
             ctx.give(a);
@@ -68,11 +67,11 @@ public:
         }
         void* act = ctx.take_tokens(I_, DType::BF16);
         if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
-            ops::skinny_swiglu(h, nw, eps, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
+            ops::skinny_gated(h, nw, eps, gate_up_.weight, ctx.T, I_, act_, act, ctx.err, ctx.stream);
         } else {
             void* x = ctx.take_tokens(hidden_, DType::BF16);           // many rows: norm once, not once per CTA
             norm.forward(ctx, h, nullptr, x, nullptr, 0);
-            if (skinny) ops::skinny_swiglu(x, nullptr, 0.f, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
+            if (skinny) ops::skinny_gated(x, nullptr, 0.f, gate_up_.weight, ctx.T, I_, act_, act, ctx.err, ctx.stream);
             else ops::tc_swiglu(x, hidden_, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
             ctx.give(x);
         }
