@@ -205,6 +205,33 @@ def test_experts_of_many_tokens_bfloat16(toy_plugin, tmp_path):
     run_cuts(engine, requests, plain, cuts, 1.5e-2)
 
 
+def test_experts_inside_a_layer_bfloat16(toy_plugin, tmp_path):
+    """A pre-norm layer whose mixer adds nothing (its output projection is zero), so that the logits are x + experts(norm(x)):
+    with few tokens the router and the experts norm the residual stream themselves and add into it, with many the norm is a
+    kernel of its own and the pairs are grouped; both against the plain implementation on the normed rows as bfloat16 holds them."""
+    import velomind_b200 as vm
+    args = {"hidden": 64, "experts": 6, "top": 2, "ff": 32, "shared_ff": 24}
+    ident = {"kind": "identity", "args": {"size": 64}}
+    quiet = {"kind": "mlstm", "args": {"hidden": 64, "heads": 1, "dim": 4, "vdim": 4, "gate_cap": 5.0, "eps": 1e-6}}
+    cfg = {"architectures": ["ProbeForCausalLM"], "hidden": 64, "vocab": 64, "limit": 4096,
+           "embedding": {"kind": "token_table", "args": {"vocab": 64, "hidden": 64}}, "final_norm": ident, "head": ident,
+           "blocks": [{"arrangement": "prenorm", "mixer": quiet, "feed_forward": {"kind": "routed_experts", "args": args}, "mixer_norm": ident,
+                       "feed_forward_norm": {"kind": "rmsnorm", "args": {"size": 64, "eps": 1e-5}}}]}
+    w = rounded_to_bf16(random_tensors(vm.weight_table(cfg), np.random.default_rng(53), 0.25))
+    w["layers.0.mixer.o"][:] = 0.0
+    folder = write_model(str(tmp_path / "layer"), cfg, w, as_bf16=True)
+    engine = vm.Engine(vm.load_model(folder, "bfloat16", "cuda:0"), 64 * 8, max_slots=3)
+    requests = S.make_requests(64, (20, 3, 150), seed=7)
+    mlp = {"router": {"top": 2}, "shared": {"ff": 24}}
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks]
+        xn = rounded_to_bf16({"x": K.rms_norm(x, w["layers.0.feed_forward_norm.weight"], 1e-5).astype(np.float32)})["x"].astype(np.float64)
+        plain[rid] = x + K.routed_experts(xn, w, "layers.0.feed_forward.", mlp)
+    cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests, tail=10), "batches": S.steps_unequal_batches(requests)}
+    run_cuts(engine, requests, plain, cuts, 1.5e-2)
+
+
 # ----------------------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def kog_folders(tmp_path_factory):

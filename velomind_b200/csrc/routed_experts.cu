@@ -103,20 +103,41 @@ __device__ __forceinline__ void warp_dot_rows(const W* const (&w)[R], const floa
 
 constexpr int ROWS_PER_WARP = 4;
 
+// A token's input row as float32 in shared memory.  norm_w == nullptr: x is the row in the activation dtype.  Otherwise x is the
+// float32 residual stream and the row is rmsnorm(x) * norm_w, rounded as the activation dtype would hold it, so that a step
+// gives the same numbers whether the norm ran here or in a kernel of its own.  `red`: 32 floats of shared memory.
+template <typename T>
+__device__ __forceinline__ void stage_row(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, int t, int hidden, float* xs,
+                                          float* red) {
+    if (norm_w == nullptr) {
+        const T* row = static_cast<const T*>(x) + (size_t)t * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(row[i]);
+        __syncthreads();
+        return;
+    }
+    const float* row = static_cast<const float*>(x) + (size_t)t * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = row[i]; xs[i] = v; ss += v * v; }
+    ss = vm_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(vm_from_float<T>(xs[i] * inv * norm_w[i]));
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------------------------------------ router
 // Router weights, bias and the shared expert's gate row are float32 (exact copies of what the checkpoint stores).
 template <typename T>
-__global__ void router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ b_router,
-                              const float* __restrict__ w_gate, int hidden, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
-                              float* __restrict__ shared_gate) {
+__global__ void router_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ w_router,
+                              const float* __restrict__ b_router, const float* __restrict__ w_gate, int hidden, int E, int top,
+                              int* __restrict__ chosen, float* __restrict__ weight, float* __restrict__ shared_gate) {
+    __shared__ float red[32];
     extern __shared__ __align__(16) float sm[];          // [hidden] input, [E] logits
     float* xs = sm;
     float* z = sm + hidden;
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(x[(size_t)t * hidden + i]);
-    __syncthreads();
+    stage_row<T>(x, norm_w, eps, t, hidden, xs, red);
     for (int e = warp; e < E + (w_gate ? 1 : 0); e += nw) {
         if (e < E) {
             const float d = warp_dot<float>(w_router + (size_t)e * hidden, xs, hidden, lane);
@@ -161,15 +182,15 @@ __global__ void router_kernel(const T* __restrict__ x, const float* __restrict__
 // ------------------------------------------------------------------------------------------------ up-projections
 // grid (row tiles, T); a warp per row r of the token's [top * ff + ff_shared] rows
 template <typename T, typename W>
-__global__ void experts_up_kernel(const T* __restrict__ x, const W* __restrict__ w_up, const W* __restrict__ w_up_shared,
-                                  const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared,
-                                  T* __restrict__ act) {
+__global__ void experts_up_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const W* __restrict__ w_up,
+                                  const W* __restrict__ w_up_shared, const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top,
+                                  int act_kind, int act_kind_shared, T* __restrict__ act) {
     extern __shared__ __align__(16) float xs[];          // [hidden]
+    __shared__ float red[32];
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = vm_to_float(x[(size_t)t * hidden + i]);
-    __syncthreads();
+    stage_row<T>(x, norm_w, eps, t, hidden, xs, red);
     const int rows = top * ff + ff_shared;
     const int r0 = (blockIdx.x * nw + warp) * ROWS_PER_WARP;
     if (r0 >= rows) return;
@@ -201,7 +222,7 @@ __global__ void experts_up_kernel(const T* __restrict__ x, const W* __restrict__
 template <typename T, typename W>
 __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restrict__ w_down, const W* __restrict__ w_down_shared,
                                     const int* __restrict__ chosen, const float* __restrict__ weight, const float* __restrict__ shared_gate,
-                                    int hidden, int ff, int ff_shared, int top, T* __restrict__ out) {
+                                    int hidden, int ff, int ff_shared, int top, T* __restrict__ out, float* __restrict__ residual) {
     extern __shared__ __align__(16) float as[];          // [top * ff + ff_shared]
     vm_pdl_launch_dependents();
     vm_pdl_wait();
@@ -234,14 +255,18 @@ __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restri
     if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i)
-            if (c0 + i < hidden) out[(size_t)t * hidden + c0 + i] = vm_from_float<T>(y[i]);
+            if (c0 + i < hidden) {
+                // into the float32 residual stream if one is given (through the activation dtype's rounding, as the unfused step adds it)
+                if (residual) residual[(size_t)t * hidden + c0 + i] += vm_to_float(vm_from_float<T>(y[i]));
+                else out[(size_t)t * hidden + c0 + i] = vm_from_float<T>(y[i]);
+            }
     }
 }
 
 template <typename T, typename W>
-int launch_experts(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared, const int* chosen,
-                   const float* weight, const float* shared_gate, int T_, int hidden, int ff, int ff_shared, int top, int act_kind,
-                   int act_kind_shared, void* act, void* out, cudaStream_t stream) {
+int launch_experts(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
+                   const void* w_down_shared, const int* chosen, const float* weight, const float* shared_gate, int T_, int hidden, int ff,
+                   int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, float* residual, cudaStream_t stream) {
     const int rows = top * ff + ff_shared;
     const int warps = 8;
     const size_t up_smem = (size_t)hidden * sizeof(float), down_smem = (size_t)rows * sizeof(float);
@@ -256,30 +281,31 @@ int launch_experts(const void* x, const void* w_up, const void* w_down, const vo
         down_raised = down_smem;
     }
     const int per_block = warps * ROWS_PER_WARP;
-    vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, (const T*)x,
+    vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, x, norm_w, eps,
                   (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, (T*)act);
     int st = vm_launch_status();
     if (st) return st;
     vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)rows * sizeof(float), stream,
-                  (const T*)act, (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, (T*)out);
+                  (const T*)act, (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, (T*)out, residual);
     return vm_launch_status();
 }
 
 }  // namespace
 
 // chosen int32 [T, top], weight float32 [T, top], shared_gate float32 [T] (written only if w_gate is given)
-VM_API int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
-                            int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream) {
+// norm_w given: x is the float32 residual stream and the router (like the experts below) norms its rows itself
+VM_API int vm_expert_router(const void* x, const float* norm_w, float eps, const float* w_router, const float* b_router, const float* w_gate, int T,
+                            int hidden, int E, int top, int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || hidden <= 0) return VM_ERR_BAD_ARG;
     const size_t smem = (size_t)(hidden + E) * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32)
-        vm_launch_pdl(router_kernel<float>, dim3(T), dim3(256), smem, stream, (const float*)x, w_router, b_router, w_gate, hidden, E, top, chosen, weight,
+        vm_launch_pdl(router_kernel<float>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, b_router, w_gate, hidden, E, top, chosen, weight,
                       shared_gate);
     else if (act_dtype == VM_BF16)
-        vm_launch_pdl(router_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, (const __nv_bfloat16*)x, w_router, b_router, w_gate, hidden, E, top,
-                      chosen, weight, shared_gate);
+        vm_launch_pdl(router_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, b_router, w_gate, hidden, E, top, chosen,
+                      weight, shared_gate);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
 }
@@ -287,20 +313,21 @@ VM_API int vm_expert_router(const void* x, const float* w_router, const float* b
 // x, out [T, hidden] and the scratch `act` [T, top * ff + ff_shared] in the activation dtype; expert weights stacked:
 // w_up [E * ff, hidden], w_down [E * hidden, ff]; the shared expert's w_up_shared [ff_shared, hidden], w_down_shared [hidden, ff_shared]
 // (ff_shared 0: none).  weight_dtype is the experts' (and the shared expert's) storage.
-VM_API int vm_experts_few_tokens(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared,
-                                 int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
-                                 int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, int act_dtype,
-                                 cudaStream_t stream) {
+// norm_w given: x is the float32 residual stream, normed here.  residual given: the result is added into it and `out` is not written.
+VM_API int vm_experts_few_tokens(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
+                                 const void* w_down_shared, int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T,
+                                 int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out,
+                                 float* residual, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hidden <= 0 || ff <= 0 || ff_shared < 0 || top <= 0) return VM_ERR_BAD_ARG;
     if (act_dtype == VM_F32 && weight_dtype == VM_F32)
-        return launch_experts<float, float>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared, top,
-                                            act_kind, act_kind_shared, act, out, stream);
+        return launch_experts<float, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared,
+                                            top, act_kind, act_kind_shared, act, out, residual, stream);
     if (act_dtype == VM_BF16 && weight_dtype == VM_BF16)
-        return launch_experts<__nv_bfloat16, __nv_bfloat16>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff,
-                                                            ff_shared, top, act_kind, act_kind_shared, act, out, stream);
+        return launch_experts<__nv_bfloat16, __nv_bfloat16>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T,
+                                                            hidden, ff, ff_shared, top, act_kind, act_kind_shared, act, out, residual, stream);
     if (act_dtype == VM_BF16 && weight_dtype == VM_F32)
-        return launch_experts<__nv_bfloat16, float>(x, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared,
-                                                    top, act_kind, act_kind_shared, act, out, stream);
+        return launch_experts<__nv_bfloat16, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff,
+                                                    ff_shared, top, act_kind, act_kind_shared, act, out, residual, stream);
     return VM_ERR_UNSUPPORTED;
 }

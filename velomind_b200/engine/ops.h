@@ -131,18 +131,20 @@ inline void mlstm_scan(const float* proj, int ld, const float* bias_i, const flo
     c.give(scratch);
 }
 
-inline void expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top, int* chosen,
-                          float* weight, float* shared_gate, DType act, cudaStream_t s) {
+// (norm_w given: x is the float32 residual stream and the kernels norm its rows themselves; residual given: the result is added into it)
+inline void expert_router(const void* x, const float* norm_w, float eps, const float* w_router, const float* b_router, const float* w_gate, int T,
+                          int hidden, int E, int top, int* chosen, float* weight, float* shared_gate, DType act, cudaStream_t s) {
     Timed t("expert_router", s);
-    check(vm_expert_router(x, w_router, b_router, w_gate, T, hidden, E, top, chosen, weight, shared_gate, code(act), s), "expert_router", s);
+    check(vm_expert_router(x, norm_w, eps, w_router, b_router, w_gate, T, hidden, E, top, chosen, weight, shared_gate, code(act), s), "expert_router", s);
 }
 
-inline void experts_few_tokens(const void* x, const DeviceTensor& up, const DeviceTensor& down, const void* up_shared, const void* down_shared,
-                               const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff, int ff_shared, int top,
-                               int act_kind, int act_kind_shared, void* act, void* out, DType act_dtype, cudaStream_t s) {
+inline void experts_few_tokens(const void* x, const float* norm_w, float eps, const DeviceTensor& up, const DeviceTensor& down, const void* up_shared,
+                               const void* down_shared, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
+                               int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, float* residual, DType act_dtype,
+                               cudaStream_t s) {
     Timed t("experts_few_tokens", s);
-    check(vm_experts_few_tokens(x, up.ptr, down.ptr, up_shared, down_shared, code(up.dtype), chosen, weight, shared_gate, T, hidden, ff, ff_shared, top,
-                                act_kind, act_kind_shared, act, out, code(act_dtype), s),
+    check(vm_experts_few_tokens(x, norm_w, eps, up.ptr, down.ptr, up_shared, down_shared, code(up.dtype), chosen, weight, shared_gate, T, hidden, ff,
+                                ff_shared, top, act_kind, act_kind_shared, act, out, residual, code(act_dtype), s),
           "experts_few_tokens", s);
     ++counters().own_launches;          // two kernels
 }

@@ -65,12 +65,14 @@ int vm_mlstm_step(const float* proj, int ld, const float* bias_i, const float* b
                   int act_dtype, cudaStream_t stream);
 
 // ---- routed_experts.cu: a routed feed-forward for few tokens
-int vm_expert_router(const void* x, const float* w_router, const float* b_router, const float* w_gate, int T, int hidden, int E, int top,
-                     int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream);
-int vm_experts_few_tokens(const void* x, const void* w_up, const void* w_down, const void* w_up_shared, const void* w_down_shared,
-                          int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
-                          int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, int act_dtype,
-                          cudaStream_t stream);
+// x [T, hidden] in the activation dtype, or (norm_w given) the float32 residual stream, whose rows the kernels then norm themselves;
+// residual given: the experts' result is added into it instead of being written to `out`
+int vm_expert_router(const void* x, const float* norm_w, float eps, const float* w_router, const float* b_router, const float* w_gate, int T,
+                     int hidden, int E, int top, int* chosen, float* weight, float* shared_gate, int act_dtype, cudaStream_t stream);
+int vm_experts_few_tokens(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
+                          const void* w_down_shared, int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T,
+                          int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out,
+                          float* residual, int act_dtype, cudaStream_t stream);
 
 // ---- rope_cache.cu
 int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,

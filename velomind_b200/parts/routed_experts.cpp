@@ -67,17 +67,58 @@ public:
 
     bool graph_safe() const override { return true; }
 
-    void forward(StepContext& ctx, const void* x, void* out) override {
+    // whether a step of this capacity groups its pairs by expert (many tokens) or streams each token's experts (few)
+    bool grouped(const StepContext& ctx) const {
+        return ctx.act_dtype == DType::BF16 && up_.dtype == DType::BF16 && hidden_ % 32 == 0 && ff_ % 32 == 0 && ctx.T_cap > GROUPED_FROM_TOKENS &&
+               !ctx.one_token_each;
+    }
+
+    // Few tokens in bfloat16: router and up-projections norm the residual stream's rows themselves, the down-projections add
+    // into it: three launches for the layer half.
+    bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
+        const float* nw;
+        float eps;
+        return norm.as_rms(&nw, &eps) && ctx.act_dtype == DType::BF16 && !grouped(ctx);
+    }
+
+    void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
+        const float* nw = nullptr;
+        float eps = 0.f;
+        norm.as_rms(&nw, &eps);
+        run_few(ctx, h, nw, eps, nullptr, h);
+    }
+
+    // the few-token path: x in the activation dtype, or (nw given) the float32 residual stream; `residual` given: added into
+    void run_few(StepContext& ctx, const void* x, const float* nw, float eps, void* out, float* residual) {
         int* chosen = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
         float* weight = static_cast<float*>(ctx.take_tokens(top_, DType::F32));
         float* sgate = gate_ ? static_cast<float*>(ctx.take_tokens(1, DType::F32)) : nullptr;
-        ops::expert_router(x, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
+        ops::expert_router(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
+                           gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
+                           ctx.stream);
+        void* act = ctx.take_tokens(static_cast<long long>(top_) * ff_ + sff_, ctx.act_dtype);
+        ops::experts_few_tokens(x, nw, eps, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T,
+                                hidden_, ff_, sff_, top_, act_, sact_, act, out, residual, ctx.act_dtype, ctx.stream);
+        ctx.give(act);
+        ctx.give(sgate);
+        ctx.give(weight);
+        ctx.give(chosen);
+    }
+
+    void forward(StepContext& ctx, const void* x, void* out) override {
+        if (!grouped(ctx)) {
+            run_few(ctx, x, nullptr, 0.f, out, nullptr);
+            return;
+        }
+        int* chosen = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
+        float* weight = static_cast<float*>(ctx.take_tokens(top_, DType::F32));
+        float* sgate = gate_ ? static_cast<float*>(ctx.take_tokens(1, DType::F32)) : nullptr;
+        ops::expert_router(x, nullptr, 0.f, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
                            gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
                            ctx.stream);
         // Many tokens (by the step's capacity, so that a bucket's steps ask for the same scratch): pairs grouped by expert, tensor-core
         // tiles per expert, the shared expert as two library products.  Few tokens: every token streams the rows of its experts.
-        if (ctx.act_dtype == DType::BF16 && up_.dtype == DType::BF16 && hidden_ % 32 == 0 && ff_ % 32 == 0 && ctx.T_cap > GROUPED_FROM_TOKENS &&
-            !ctx.one_token_each) {
+        {
             float* shared_y = nullptr;
             if (sff_ > 0) {
                 void* u = ctx.take_tokens(sff_, DType::BF16);
@@ -115,13 +156,6 @@ public:
             ctx.give(chosen);
             return;
         }
-        void* act = ctx.take_tokens(static_cast<long long>(top_) * ff_ + sff_, ctx.act_dtype);
-        ops::experts_few_tokens(x, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T, hidden_,
-                                ff_, sff_, top_, act_, sact_, act, out, ctx.act_dtype, ctx.stream);
-        ctx.give(act);
-        ctx.give(sgate);
-        ctx.give(weight);
-        ctx.give(chosen);
     }
 
     static constexpr int GROUPED_FROM_TOKENS = 64;      // a step's capacity above which the pairs are grouped by expert
