@@ -13,6 +13,7 @@
 #include <iostream>
 #include <sys/stat.h>
 
+#include "velomind_b200/kernels.h"
 #include "velomind_b200/velomind.h"
 
 namespace vmb {
@@ -59,7 +60,9 @@ int trace_main(int argc, char** argv) {
     ::mkdir(out_dir.c_str(), 0777);
     auto model = load_model(model_dir, compute_dtype(dtype), device);
     EngineOptions o;
-    o.max_tokens = max_tokens;
+    // --max-tokens counts the tokens of live requests; every live request may leave the last of its pages part empty, so
+    // the pool gets a page more for each of up to 64 requests that may be live at once
+    o.max_tokens = max_tokens + 64ll * VM_PAGE_TOKENS;
     Engine engine(model, o);
     std::map<std::string, int> slots;
     std::string line;
