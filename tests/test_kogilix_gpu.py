@@ -389,6 +389,17 @@ def test_greedy_generation_through_the_entry_point(kog_folders):
     assert [r.tokens for r in again] == [r.tokens for r in out]
 
 
+def test_the_console_program_generates(kog_folders):
+    """The library's command line takes the model folder as it takes any other: token ids in, greedy tokens out."""
+    cfg, w = K.read_model(kog_folders["a"])
+    want = K.generate_greedy(cfg, w, [5, 6, 7, 8], 5)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "smollm2_chat"), "--model", kog_folders["a"], "--dtype", "float32", "--temp", "0",
+                           "--max-tokens", "5", "--prompt-ids", "5,6,7,8"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = [ln for ln in proc.stdout.splitlines() if ln.startswith("Output: ")][0]
+    assert line == "Output: " + "".join(f"[{t}]" for t in want)
+
+
 def test_trace_replay_program(kog_folders, tmp_path):
     cfg, w = K.read_model(kog_folders["a"])
     requests = S.make_requests(cfg["vocab"], (40, 3, 90), seed=12)
