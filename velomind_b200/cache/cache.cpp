@@ -68,10 +68,13 @@ PageBook::PageBook(const CacheNeed& need_, int n_pages_, int max_slots_, int max
       table_(static_cast<size_t>(max_slots_) * max_blocks_, -1) {
     if (need.kind != CacheNeed::All && need.kind != CacheNeed::Window) throw CacheError("a cache group holds keys and values; a need of kind 'none' has none");
     if (need.kind == CacheNeed::Window && need.window <= 0) throw CacheError("a window group needs window > 0");
-    if (need.value_dim != 0 && need.key_dim != need.value_dim)      // value_dim 0: one row per token and no second one (a latent that serves as both)
-        throw CacheError(format("a cache group stores keys and values of one head size; a mixer asked for keys of %d and values of %d", need.key_dim,
+    if (need.key_dim <= 0 || need.value_dim < 0)                    // value_dim 0: one row per token and no second one (a latent that serves as both)
+        throw CacheError(format("a cache group stores keys of a positive size and values of a size >= 0; a mixer asked for %d and %d", need.key_dim,
                                 need.value_dim));
+    if (need.keep_first < 0 || (need.keep_first > 0 && need.kind != CacheNeed::Window)) throw CacheError("keep_first belongs to a window group and is >= 0");
 }
+
+int PageBook::kept_blocks() const { return need.kind == CacheNeed::Window ? ceil_div(need.keep_first, VM_PAGE_TOKENS) : 0; }
 
 int PageBook::pages_needed(int slot, int new_len) const { return std::max(0, ceil_div(new_len, VM_PAGE_TOKENS) - blocks_end[slot]); }
 
@@ -89,8 +92,9 @@ void PageBook::ensure(int slot, int new_len) {
 void PageBook::trim(int slot, int length) {
     if (need.kind != CacheNeed::Window) return;
     // the next query sits at position `length` or later and sees keys at positions > length - window
+    // (the blocks of the first keep_first tokens stay: every later query sees them)
     const int first_needed = std::max(0, length - need.window + 1);
-    int b = blocks_begin[slot];
+    int b = std::max(blocks_begin[slot], std::min(kept_blocks(), blocks_end[slot]));
     while (b < blocks_end[slot] && (b + 1) * VM_PAGE_TOKENS <= first_needed) {
         int& entry = table_[static_cast<size_t>(slot) * max_blocks + b];
         pages.give(entry);
@@ -102,7 +106,8 @@ void PageBook::trim(int slot, int length) {
 }
 
 void PageBook::release(int slot) {
-    for (int b = blocks_begin[slot]; b < blocks_end[slot]; ++b) {
+    for (int b = 0; b < blocks_end[slot]; ++b) {
+        if (!holds(slot, b)) continue;
         int& entry = table_[static_cast<size_t>(slot) * max_blocks + b];
         pages.give(entry);
         entry = -1;
@@ -202,9 +207,10 @@ void CacheBook::check() const {
         for (int s = 0; s < max_slots; ++s)
             for (int b = 0; b < g.max_blocks; ++b) {
                 const int pg = g.table_row(s)[b];
-                const bool inside = g.blocks_begin[s] <= b && b < g.blocks_end[s];
+                const bool inside = g.holds(s, b);
                 if ((pg >= 0) != inside)
-                    throw CacheError(format("slot %d block %d: page %d but live range is [%d, %d)", s, b, pg, g.blocks_begin[s], g.blocks_end[s]));
+                    throw CacheError(format("slot %d block %d: page %d but live range is [%d, %d) and %d kept blocks", s, b, pg, g.blocks_begin[s],
+                                            g.blocks_end[s], g.kept_blocks()));
                 if (pg >= 0) {
                     if (!held.insert(pg).second) throw CacheError(format("cache page %d is held twice", pg));
                     if (!slots.is_held(s)) throw CacheError(format("cache page %d belongs to closed slot %d", pg, s));
@@ -224,7 +230,8 @@ SequenceCache::SequenceCache(const std::vector<CacheNeed>& needs, const std::vec
         GroupStorage s;
         s.layer_bytes = static_cast<size_t>(book.n_pages) * need.kv_heads * VM_PAGE_TOKENS * need.key_dim * dtype_size(dtype);
         s.k = std::make_unique<DeviceBuffer>(s.layer_bytes * book.layers_in_group[g], /*zero=*/true);
-        if (need.value_dim > 0) s.v = std::make_unique<DeviceBuffer>(s.layer_bytes * book.layers_in_group[g], /*zero=*/true);
+        s.value_layer_bytes = static_cast<size_t>(book.n_pages) * need.kv_heads * VM_PAGE_TOKENS * need.value_dim * dtype_size(dtype);
+        if (need.value_dim > 0) s.v = std::make_unique<DeviceBuffer>(s.value_layer_bytes * book.layers_in_group[g], /*zero=*/true);
         storage.push_back(std::move(s));
     }
     state.resize(needs.size());
@@ -253,7 +260,7 @@ int SequenceCache::open() {
 void* SequenceCache::k_pages(int group, int layer) const { return static_cast<char*>(storage[group].k->ptr) + storage[group].layer_bytes * layer; }
 void* SequenceCache::v_pages(int group, int layer) const {
     if (!storage[group].v) return nullptr;         // a group that keeps one row per token
-    return static_cast<char*>(storage[group].v->ptr) + storage[group].layer_bytes * layer;
+    return static_cast<char*>(storage[group].v->ptr) + storage[group].value_layer_bytes * layer;
 }
 
 }  // namespace vmb

@@ -19,6 +19,13 @@ __device__ __forceinline__ float expert_act(float z, int kind) {
     return z / (1.0f + expf(-z));
 }
 
+// the clamped gated unit: g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1)
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
 // dot product of a weight row with a float32 vector in shared memory, summed over a warp
 template <typename W> __device__ __forceinline__ float warp_dot(const W* __restrict__ w, const float* __restrict__ x, int n, int lane) {
     float acc = 0.f;
@@ -179,12 +186,94 @@ __global__ void router_kernel(const void* __restrict__ x, const float* __restric
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ router with scores over all outputs
+//   s = softmax(z) over all n_out outputs;  choice = s + correction (the correction steers the choice, not the weights)
+//   outputs form `group_count` equal groups of neighbours; a group's score is its largest choice score; only outputs of the
+//   `group_keep` best groups can be chosen (the lowest group index wins a tie, as the lowest output index does below)
+//   the `top` largest choice scores are chosen; weight = s * scale, not renormalised
+template <typename T>
+__global__ void router_scored_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ w_router,
+                                     const float* __restrict__ correction, int hidden, int n_out, int top, int group_count, int group_keep,
+                                     float scale, int* __restrict__ chosen, float* __restrict__ weight) {
+    __shared__ float red[32];
+    extern __shared__ __align__(16) float sm[];          // [hidden] input, [n_out] scores, [n_out] choice scores, [group_count] group scores
+    float* xs = sm;
+    float* sc = sm + hidden;
+    float* ch = sc + n_out;
+    float* gs = ch + n_out;
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    stage_row<T>(x, norm_w, eps, t, hidden, xs, red);
+    for (int e = warp; e < n_out; e += nw) {
+        const float d = warp_dot<float>(w_router + (size_t)e * hidden, xs, hidden, lane);
+        if (lane == 0) sc[e] = d;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, sc[e]);
+    mx = vm_warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_out; e += 32) sum += expf(sc[e] - mx);
+    sum = vm_warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < n_out; e += 32) {
+        const float p = expf(sc[e] - mx) * inv;
+        sc[e] = p;
+        ch[e] = p + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (group_count > 1 && group_keep < group_count) {
+        const int per = n_out / group_count;
+        for (int g = lane; g < group_count; g += 32) {
+            float best = -INFINITY;
+            for (int i = 0; i < per; ++i) best = fmaxf(best, ch[g * per + i]);
+            gs[g] = best;
+        }
+        __syncwarp();
+        // a group stays if fewer than group_keep groups come before it in the order (score descending, index ascending)
+        for (int g = lane; g < group_count; g += 32) {
+            int before = 0;
+            for (int o = 0; o < group_count; ++o) before += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+            if (before >= group_keep)
+                for (int i = 0; i < per; ++i) ch[g * per + i] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_out; e += 32) {
+            const float v = ch[e];
+            if (v > best) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) at = 0;                      // fewer eligible outputs than `top` (a configuration the host refuses)
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = at;
+            weight[(size_t)t * top + k] = sc[at] * scale;
+            ch[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ up-projections
-// grid (row tiles, T); a warp per row r of the token's [top * ff + ff_shared] rows
+// grid (row tiles, T); a warp per row r of the token's [top * ff + ff_shared] rows.  An act row has `act_cols` columns:
+// those rows and, where identity experts exist (E_real < the router's outputs), the token's input row behind them.
+// glu: an expert's up matrix is [2 * ff, hidden], gate rows first, and row r is glu_clamped(gate_r . x, up_r . x).
 template <typename T, typename W>
 __global__ void experts_up_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const W* __restrict__ w_up,
                                   const W* __restrict__ w_up_shared, const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top,
-                                  int act_kind, int act_kind_shared, T* __restrict__ act) {
+                                  int act_kind, int act_kind_shared, int E_real, int glu, float limit, float alpha, int act_cols,
+                                  T* __restrict__ act) {
     extern __shared__ __align__(16) float xs[];          // [hidden]
     __shared__ float red[32];
     vm_pdl_launch_dependents();
@@ -192,28 +281,44 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     stage_row<T>(x, norm_w, eps, t, hidden, xs, red);
     const int rows = top * ff + ff_shared;
+    if (blockIdx.x == 0 && act_cols > rows)               // the input row, for the identity experts of the down kernel
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) act[(size_t)t * act_cols + rows + i] = vm_from_float<T>(xs[i]);
     const int r0 = (blockIdx.x * nw + warp) * ROWS_PER_WARP;
     if (r0 >= rows) return;
     const W* wrow[ROWS_PER_WARP];
+    const W* urow[ROWS_PER_WARP];
     int kind[ROWS_PER_WARP];
+    bool routed[ROWS_PER_WARP], skip[ROWS_PER_WARP];
+    const int per = glu ? 2 * ff : ff;                    // rows of one expert's up matrix
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
         const int r = min(r0 + i, rows - 1);              // (a row past the end repeats the last one and is not stored)
-        if (r < top * ff) {
-            const int e = chosen[(size_t)t * top + r / ff];
-            wrow[i] = w_up + ((size_t)e * ff + r % ff) * hidden;
+        routed[i] = r < top * ff;
+        skip[i] = false;
+        if (routed[i]) {
+            int e = chosen[(size_t)t * top + r / ff];
+            if (e >= E_real) { skip[i] = true; e = 0; }   // an identity expert has no rows: zeros
+            wrow[i] = w_up + ((size_t)e * per + r % ff) * hidden;
+            urow[i] = wrow[i] + (size_t)ff * hidden;
             kind[i] = act_kind;
         } else {
-            wrow[i] = w_up_shared + (size_t)(r - top * ff) * hidden;
+            wrow[i] = urow[i] = w_up_shared + (size_t)(r - top * ff) * hidden;
             kind[i] = act_kind_shared;
         }
     }
-    float d[ROWS_PER_WARP];
+    float d[ROWS_PER_WARP], u[ROWS_PER_WARP];
     warp_dot_rows<W, ROWS_PER_WARP>(wrow, xs, hidden, lane, d);
+    if (glu) warp_dot_rows<W, ROWS_PER_WARP>(urow, xs, hidden, lane, u);
     if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i)
-            if (r0 + i < rows) act[(size_t)t * rows + r0 + i] = vm_from_float<T>(expert_act(d[i], kind[i]));
+            if (r0 + i < rows) {
+                float v;
+                if (skip[i]) v = 0.f;
+                else if (glu && routed[i]) v = glu_clamped(vm_to_float(vm_from_float<T>(d[i])), vm_to_float(vm_from_float<T>(u[i])), limit, alpha);
+                else v = expert_act(d[i], kind[i]);
+                act[(size_t)t * act_cols + r0 + i] = vm_from_float<T>(v);
+            }
     }
 }
 
@@ -222,13 +327,14 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
 template <typename T, typename W>
 __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restrict__ w_down, const W* __restrict__ w_down_shared,
                                     const int* __restrict__ chosen, const float* __restrict__ weight, const float* __restrict__ shared_gate,
-                                    int hidden, int ff, int ff_shared, int top, T* __restrict__ out, float* __restrict__ residual) {
-    extern __shared__ __align__(16) float as[];          // [top * ff + ff_shared]
+                                    int hidden, int ff, int ff_shared, int top, int E_real, int act_cols, T* __restrict__ out,
+                                    float* __restrict__ residual) {
+    extern __shared__ __align__(16) float as[];          // [act_cols]: top * ff + ff_shared, then (identity experts) the input row
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int rows = top * ff + ff_shared;
-    for (int i = threadIdx.x; i < rows; i += blockDim.x) as[i] = vm_to_float(act[(size_t)t * rows + i]);
+    for (int i = threadIdx.x; i < act_cols; i += blockDim.x) as[i] = vm_to_float(act[(size_t)t * act_cols + i]);
     __syncthreads();
     const int c0 = (blockIdx.x * nw + warp) * ROWS_PER_WARP;
     if (c0 >= hidden) return;
@@ -237,6 +343,12 @@ __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restri
     float d[ROWS_PER_WARP];
     for (int k = 0; k < top; ++k) {
         const int e = chosen[(size_t)t * top + k];
+        if (e >= E_real) {                                // an identity expert: the input itself, times the weight
+            const float wk = weight[(size_t)t * top + k];
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) y[i] = fmaf(wk, as[rows + min(c0 + i, hidden - 1)], y[i]);
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i) wrow[i] = w_down + ((size_t)e * hidden + min(c0 + i, hidden - 1)) * ff;
         warp_dot_rows<W, ROWS_PER_WARP>(wrow, as + k * ff, ff, lane, d);
@@ -266,10 +378,12 @@ __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restri
 template <typename T, typename W>
 int launch_experts(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
                    const void* w_down_shared, const int* chosen, const float* weight, const float* shared_gate, int T_, int hidden, int ff,
-                   int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out, float* residual, cudaStream_t stream) {
+                   int ff_shared, int top, int act_kind, int act_kind_shared, int E_real, int n_identity, int glu, float limit, float alpha, void* act,
+                   void* out, float* residual, cudaStream_t stream) {
     const int rows = top * ff + ff_shared;
+    const int act_cols = rows + (n_identity > 0 ? hidden : 0);
     const int warps = 8;
-    const size_t up_smem = (size_t)hidden * sizeof(float), down_smem = (size_t)rows * sizeof(float);
+    const size_t up_smem = (size_t)hidden * sizeof(float), down_smem = (size_t)act_cols * sizeof(float);
     if (up_smem > 200 * 1024 || down_smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
     static size_t up_raised = 48 * 1024, down_raised = 48 * 1024;       // per instantiation
     if (up_smem > up_raised) {
@@ -282,11 +396,12 @@ int launch_experts(const void* x, const float* norm_w, float eps, const void* w_
     }
     const int per_block = warps * ROWS_PER_WARP;
     vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, x, norm_w, eps,
-                  (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, (T*)act);
+                  (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, E_real, glu, limit, alpha, act_cols,
+                  (T*)act);
     int st = vm_launch_status();
     if (st) return st;
-    vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)rows * sizeof(float), stream,
-                  (const T*)act, (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, (T*)out, residual);
+    vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + per_block - 1) / per_block, T_), dim3(warps * 32), down_smem, stream, (const T*)act,
+                  (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, E_real, act_cols, (T*)out, residual);
     return vm_launch_status();
 }
 
@@ -310,24 +425,61 @@ VM_API int vm_expert_router(const void* x, const float* norm_w, float eps, const
     return vm_launch_status();
 }
 
-// x, out [T, hidden] and the scratch `act` [T, top * ff + ff_shared] in the activation dtype; expert weights stacked:
-// w_up [E * ff, hidden], w_down [E * hidden, ff]; the shared expert's w_up_shared [ff_shared, hidden], w_down_shared [hidden, ff_shared]
-// (ff_shared 0: none).  weight_dtype is the experts' (and the shared expert's) storage.
+// x, out [T, hidden] and the scratch `act` [T, vm_experts_act_cols(...)] in the activation dtype; expert weights stacked:
+// w_up [E * ff, hidden] (glu: [E * 2 * ff, hidden], an expert's gate rows before its up rows), w_down [E * hidden, ff]; the shared expert's
+// w_up_shared [ff_shared, hidden], w_down_shared [hidden, ff_shared] (ff_shared 0: none).  weight_dtype is the experts' storage.
+// A chosen index >= E names an identity expert (n_identity of them): its result is the input row.  glu: act = glu_clamped(gate, up)
+// with `limit` and `alpha`; else act_kind.
 // norm_w given: x is the float32 residual stream, normed here.  residual given: the result is added into it and `out` is not written.
+VM_API long long vm_experts_act_cols(int hidden, int ff, int ff_shared, int top, int n_identity) {
+    return (long long)top * ff + ff_shared + (n_identity > 0 ? hidden : 0);
+}
+
+VM_API int vm_experts_few_tokens_glu(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
+                                     const void* w_down_shared, int weight_dtype, const int* chosen, const float* weight, const float* shared_gate,
+                                     int T, int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, int E, int n_identity,
+                                     int glu, float limit, float alpha, void* act, void* out, float* residual, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hidden <= 0 || ff <= 0 || ff_shared < 0 || top <= 0 || E <= 0 || n_identity < 0) return VM_ERR_BAD_ARG;
+    if (act_dtype == VM_F32 && weight_dtype == VM_F32)
+        return launch_experts<float, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared,
+                                            top, act_kind, act_kind_shared, E, n_identity, glu, limit, alpha, act, out, residual, stream);
+    if (act_dtype == VM_BF16 && weight_dtype == VM_BF16)
+        return launch_experts<__nv_bfloat16, __nv_bfloat16>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T,
+                                                            hidden, ff, ff_shared, top, act_kind, act_kind_shared, E, n_identity, glu, limit, alpha, act,
+                                                            out, residual, stream);
+    if (act_dtype == VM_BF16 && weight_dtype == VM_F32)
+        return launch_experts<__nv_bfloat16, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff,
+                                                    ff_shared, top, act_kind, act_kind_shared, E, n_identity, glu, limit, alpha, act, out, residual,
+                                                    stream);
+    return VM_ERR_UNSUPPORTED;
+}
+
+// the same for experts of one up matrix and an activation, every chosen index a real expert
 VM_API int vm_experts_few_tokens(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
                                  const void* w_down_shared, int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T,
                                  int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out,
                                  float* residual, int act_dtype, cudaStream_t stream) {
+    return vm_experts_few_tokens_glu(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, weight_dtype, chosen, weight, shared_gate, T, hidden, ff,
+                                     ff_shared, top, act_kind, act_kind_shared, 0x7fffffff, 0, 0, 0.f, 0.f, act, out, residual, act_dtype, stream);
+}
+
+// chosen int32 [T, top] (an index >= the number of real experts names an identity expert), weight float32 [T, top]; w_router float32
+// [n_out, hidden], correction float32 [n_out] or null; group_count must divide n_out
+VM_API int vm_expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                                   int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, int act_dtype,
+                                   cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (hidden <= 0 || ff <= 0 || ff_shared < 0 || top <= 0) return VM_ERR_BAD_ARG;
-    if (act_dtype == VM_F32 && weight_dtype == VM_F32)
-        return launch_experts<float, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff, ff_shared,
-                                            top, act_kind, act_kind_shared, act, out, residual, stream);
-    if (act_dtype == VM_BF16 && weight_dtype == VM_BF16)
-        return launch_experts<__nv_bfloat16, __nv_bfloat16>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T,
-                                                            hidden, ff, ff_shared, top, act_kind, act_kind_shared, act, out, residual, stream);
-    if (act_dtype == VM_BF16 && weight_dtype == VM_F32)
-        return launch_experts<__nv_bfloat16, float>(x, norm_w, eps, w_up, w_down, w_up_shared, w_down_shared, chosen, weight, shared_gate, T, hidden, ff,
-                                                    ff_shared, top, act_kind, act_kind_shared, act, out, residual, stream);
-    return VM_ERR_UNSUPPORTED;
+    if (n_out <= 0 || top <= 0 || hidden <= 0 || group_count <= 0 || n_out % group_count || group_keep <= 0 || group_keep > group_count) return VM_ERR_BAD_ARG;
+    if (top > (n_out / group_count) * group_keep) return VM_ERR_BAD_ARG;
+    const size_t smem = (size_t)(hidden + 2 * n_out + group_count) * sizeof(float);
+    if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    if (act_dtype == VM_F32)
+        vm_launch_pdl(router_scored_kernel<float>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top, group_count,
+                      group_keep, scale, chosen, weight);
+    else if (act_dtype == VM_BF16)
+        vm_launch_pdl(router_scored_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top,
+                      group_count, group_keep, scale, chosen, weight);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
 }

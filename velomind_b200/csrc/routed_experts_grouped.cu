@@ -17,6 +17,7 @@ constexpr int TM = 64, TN = 64, TK = 32, PAD = 8;       // tile of rows, of colu
 constexpr int GROUP_THREADS = 1024;
 
 __device__ __forceinline__ float act_of(float z, int kind) {
+    if (kind < 0) return z;                                  // no activation
     if (kind == VM_ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
     if (kind == VM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     return z / (1.0f + expf(-z));
@@ -134,6 +135,7 @@ experts_up_grouped_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
         const int tok = token_of_row[row0 + r];
         return tok >= 0 ? x + (size_t)tok * hidden : nullptr;
     };
+    // (`ff` here is the number of rows of one expert's up matrix: twice the expert's size for gated experts)
     tile_product(a_row, w_up + (size_t)e * ff * hidden, ff, hidden, n0, [&](int r, int n, float c0, float c1) {
         __nv_bfloat16* dst = act + (size_t)(row0 + r) * ff + n;
         if (n + 1 < ff) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(act_of(c0, act_kind), act_of(c1, act_kind));
@@ -155,9 +157,10 @@ experts_down_grouped_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bf
     });
 }
 
+// (x and chosen given: a pair whose index is E or more is an identity expert, its result the token's input row)
 __global__ void experts_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
                                        const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int T, int hidden, int top,
-                                       __nv_bfloat16* __restrict__ out) {
+                                       const __nv_bfloat16* __restrict__ x, const int* __restrict__ chosen, int E, __nv_bfloat16* __restrict__ out) {
     const size_t n = (size_t)T * hidden;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / hidden), c = (int)(i - (size_t)t * hidden);
@@ -165,6 +168,7 @@ __global__ void experts_combine_kernel(const float* __restrict__ y, const int* _
         for (int k = 0; k < top; ++k) {
             const int row = row_of_pair[(size_t)t * top + k];
             if (row >= 0) acc = fmaf(weight[(size_t)t * top + k], y[(size_t)row * hidden + c], acc);
+            else if (x && chosen[(size_t)t * top + k] >= E) acc = fmaf(weight[(size_t)t * top + k], __bfloat162float(x[i]), acc);
         }
         if (shared_y) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared_y[i], acc);
         out[i] = __float2bfloat16_rn(acc);
@@ -183,6 +187,18 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
     }
 }
 
+// act[row, i] = glu_clamped(gate_up[row, i], gate_up[row, ff + i]); rows of padding hold zeros and give zeros
+__global__ void glu_rows_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, size_t n, int ff, float limit, float alpha) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / ff;
+        const int c = (int)(i - row * ff);
+        float g = __bfloat162float(gate_up[row * 2 * ff + c]), u = __bfloat162float(gate_up[row * 2 * ff + ff + c]);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        act[i] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
 template <typename T> __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int kind) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = vm_from_float<T>(act_of(vm_to_float(in[i]), kind));
@@ -193,74 +209,90 @@ template <typename T> __global__ void activation_kernel(const T* __restrict__ in
 // rows the grouped layout may need for T tokens: every pair, plus padding of each expert's run to whole tiles
 VM_API long long vm_experts_grouped_rows(int T, int top, int E) { return ((long long)T * top + (long long)E * (TM - 1) + TM - 1) / TM * TM; }
 
-// x, out [T, hidden] bfloat16; w_up [E * ff, hidden], w_down [E * hidden, ff] bfloat16; chosen / weight [T, top];
-// scratch: row_of_pair int [T * top], token_of_row int [row_cap], expert_of_tile int [row_cap / 64], act bf16 [row_cap, ff],
-// y float32 [row_cap, hidden]; shared_y float32 [T, hidden] (or null) is added times shared_gate [T] (or 1).
-// hidden and ff must be multiples of 32.
-VM_API int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
-                              const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
-                              int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (hidden % TK || ff % TK || top <= 0 || E <= 0) return VM_ERR_UNSUPPORTED;
-    if (row_cap % TM || row_cap < vm_experts_grouped_rows(T, top, E)) return VM_ERR_BAD_ARG;
-    if ((size_t)2 * E * sizeof(int) > 48 * 1024) return VM_ERR_UNSUPPORTED;
-    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, TM, row_of_pair, token_of_row,
-                                                                                  expert_of_tile);
-    int st = vm_launch_status();
-    if (st) return st;
-    // tiles the step can need at most (the capacity may be larger)
-    const int tiles = (int)(vm_experts_grouped_rows(T, top, E) / TM);
-    experts_up_grouped_kernel<<<dim3(tiles, (ff + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_up, token_of_row,
-                                                                                  expert_of_tile, hidden, ff, act_kind, (__nv_bfloat16*)act);
-    st = vm_launch_status();
-    if (st) return st;
-    experts_down_grouped_kernel<<<dim3(tiles, (hidden + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down,
-                                                                                        expert_of_tile, hidden, ff, y);
-    st = vm_launch_status();
-    if (st) return st;
-    const size_t n = (size_t)T * hidden;
-    const size_t want = (n + 255) / 256;
-    experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, weight, shared_y, shared_gate, T, hidden, top,
-                                                                                         (__nv_bfloat16*)out);
-    return vm_launch_status();
-}
-
-// The same with the experts' products on tcgen05 (csrc/tc_gemm.cu, grouped): runs padded to tiles of 128 rows, the rows gathered
-// into x_sorted [row_cap, hidden] first.  row_cap from vm_experts_grouped_rows_tiled(T, top, E, 128); hidden and ff multiples of 8.
 VM_API long long vm_experts_grouped_rows_tiled(int T, int top, int E, int tile) {
     return ((long long)T * top + (long long)E * (tile - 1) + tile - 1) / tile * tile;
 }
 
-VM_API int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
-                                 const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
-                                 int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, float* y, void* out, int* err,
-                                 cudaStream_t stream) {
+// x, out [T, hidden] bfloat16; w_up [E * ff, hidden] (glu: [E * 2 * ff, hidden], gate rows before up rows), w_down [E * hidden, ff] bfloat16;
+// chosen / weight [T, top] (an index >= E: an identity expert, when n_identity > 0);
+// scratch: row_of_pair int [T * top], token_of_row int [row_cap], expert_of_tile int [row_cap / tile], act bf16 [row_cap, ff],
+// gate_up bf16 [row_cap, 2 * ff] (glu only), y float32 [row_cap, hidden]; shared_y float32 [T, hidden] (or null) is added times shared_gate [T] (or 1).
+// x_sorted given (bf16 [row_cap, hidden]): the products run on tcgen05 in tiles of 128 rows (row_cap from vm_experts_grouped_rows_tiled(..., 128);
+// hidden and ff multiples of 8); else on mma.sync in tiles of 64 (row_cap from vm_experts_grouped_rows; multiples of 32).
+VM_API int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                                  const float* shared_gate, int T, int hidden, int ff, int top, int E, int n_identity, int act_kind, int glu, float limit,
+                                  float alpha, int row_cap, int* row_of_pair, int* token_of_row, int* expert_of_tile, void* x_sorted, void* act,
+                                  void* gate_up, float* y, void* out, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
-    constexpr int TILE = 128;
-    if (hidden % 8 || ff % 8 || top <= 0 || E <= 0) return VM_ERR_UNSUPPORTED;
-    if (row_cap % TILE || row_cap < vm_experts_grouped_rows_tiled(T, top, E, TILE)) return VM_ERR_BAD_ARG;
+    const bool tc = x_sorted != nullptr;
+    const int tile = tc ? 128 : TM;
+    if (top <= 0 || E <= 0 || n_identity < 0 || (glu && !gate_up)) return VM_ERR_BAD_ARG;
+    if (tc ? (hidden % 8 || ff % 8) : (hidden % TK || ff % TK)) return VM_ERR_UNSUPPORTED;
+    const long long need = tc ? vm_experts_grouped_rows_tiled(T, top, E, tile) : vm_experts_grouped_rows(T, top, E);
+    if (row_cap % tile || row_cap < need) return VM_ERR_BAD_ARG;
     if ((size_t)2 * E * sizeof(int) > 48 * 1024) return VM_ERR_UNSUPPORTED;
-    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, TILE, row_of_pair, token_of_row,
+    group_pairs_kernel<<<1, GROUP_THREADS, (size_t)2 * E * sizeof(int), stream>>>(chosen, T * top, top, E, row_cap, tile, row_of_pair, token_of_row,
                                                                                   expert_of_tile);
     int st = vm_launch_status();
     if (st) return st;
-    const int rows = (int)vm_experts_grouped_rows_tiled(T, top, E, TILE);      // rows this step can need at most (the capacity may be larger)
-    {
+    const int rows = (int)need;                 // rows this step can need at most (the capacity may be larger)
+    const int n_up = glu ? 2 * ff : ff;
+    void* up_out = glu ? gate_up : act;
+    const int up_act = glu ? -1 : act_kind;
+    if (tc) {
         const size_t n = (size_t)rows * (hidden / 8), want = (n + 255) / 256;
         gather_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)x, token_of_row, rows, hidden,
                                                                                          (__nv_bfloat16*)x_sorted);
         st = vm_launch_status();
         if (st) return st;
+        st = vm_tc_grouped_linear(x_sorted, hidden, w_up, rows, n_up, hidden, E, expert_of_tile, up_out, n_up, 0, up_act, err, stream);
+        if (st) return st;
+    } else {
+        experts_up_grouped_kernel<<<dim3(rows / TM, (n_up + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_up,
+                                                                                            token_of_row, expert_of_tile, hidden, n_up, up_act,
+                                                                                            (__nv_bfloat16*)up_out);
+        st = vm_launch_status();
+        if (st) return st;
     }
-    st = vm_tc_grouped_linear(x_sorted, hidden, w_up, rows, ff, hidden, E, expert_of_tile, act, ff, 0, act_kind, err, stream);
-    if (st) return st;
-    st = vm_tc_grouped_linear(act, ff, w_down, rows, hidden, ff, E, expert_of_tile, y, hidden, 1, -1, err, stream);
-    if (st) return st;
+    if (glu) {
+        const size_t n = (size_t)rows * ff, want = (n + 255) / 256;
+        glu_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, n, ff, limit, alpha);
+        st = vm_launch_status();
+        if (st) return st;
+    }
+    if (tc) {
+        st = vm_tc_grouped_linear(act, ff, w_down, rows, hidden, ff, E, expert_of_tile, y, hidden, 1, -1, err, stream);
+        if (st) return st;
+    } else {
+        experts_down_grouped_kernel<<<dim3(rows / TM, (hidden + TN - 1) / TN), 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down,
+                                                                                                expert_of_tile, hidden, ff, y);
+        st = vm_launch_status();
+        if (st) return st;
+    }
     const size_t n = (size_t)T * hidden;
     const size_t want = (n + 255) / 256;
     experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, weight, shared_y, shared_gate, T, hidden, top,
+                                                                                         n_identity > 0 ? (const __nv_bfloat16*)x : nullptr, chosen, E,
                                                                                          (__nv_bfloat16*)out);
     return vm_launch_status();
+}
+
+// experts of one up matrix and an activation, every chosen index a real expert: on mma.sync tiles ...
+VM_API int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                              const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                              int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream) {
+    return vm_experts_grouped_glu(x, w_up, w_down, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, E, 0, act_kind, 0, 0.f, 0.f, row_cap,
+                                  row_of_pair, token_of_row, expert_of_tile, nullptr, act, nullptr, y, out, nullptr, stream);
+}
+
+// ... and on tcgen05 (csrc/tc_gemm.cu, grouped): runs padded to tiles of 128 rows, the rows gathered into x_sorted [row_cap, hidden] first
+VM_API int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                                 const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
+                                 int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, float* y, void* out, int* err,
+                                 cudaStream_t stream) {
+    if (!x_sorted) return VM_ERR_BAD_ARG;
+    return vm_experts_grouped_glu(x, w_up, w_down, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, E, 0, act_kind, 0, 0.f, 0.f, row_cap,
+                                  row_of_pair, token_of_row, expert_of_tile, x_sorted, act, nullptr, y, out, err, stream);
 }
 
 VM_API int vm_activation(const void* in, void* out, long long n, int kind, int act_dtype, cudaStream_t stream) {

@@ -147,6 +147,21 @@ DeviceTensor BindContext::upload_stacked(const std::vector<const HostTensor*>& p
     return d;
 }
 
+DeviceTensor BindContext::upload_ints(const std::vector<int>& values) {
+    HostTensor t;
+    t.dtype = DType::I32;
+    t.shape = {static_cast<long long>(values.size())};
+    t.data = reinterpret_cast<const uint8_t*>(values.data());
+    t.nbytes = values.size() * sizeof(int);
+    DeviceTensor d;
+    d.dtype = DType::I32;
+    d.shape = t.shape;
+    d.owner = std::make_shared<DeviceBuffer>(t.nbytes);
+    d.ptr = d.owner->ptr;
+    copy_in(d.ptr, t, DType::I32, stream);
+    return d;
+}
+
 DeviceTensor BindContext::upload_floats(const std::vector<float>& values) {
     HostTensor t;
     t.dtype = DType::F32;
@@ -474,6 +489,16 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
     check(vm_attention_generic(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.seq_of_token, out, ctx.T, H,
                                Hkv, D, scale, window, kv.n_pages, code(ctx.act_dtype), ctx.err, s),
           "attention_generic", s);
+}
+
+void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int Dk, int Dv, float scale,
+                      const BiasedMask& mask) {
+    cudaStream_t s = ctx.stream;
+    Timed t("attention_biased_generic", s);
+    check(vm_attention_biased_generic(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.seq_of_token, mask.rel,
+                                      mask.bucket_of, mask.far, out, ctx.T, H, Hkv, Dk, Dv, scale, mask.window, mask.keep_first, kv.n_pages,
+                                      code(ctx.act_dtype), ctx.err, s),
+          "attention_biased_generic", s);
 }
 
 }  // namespace ops

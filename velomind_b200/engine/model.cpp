@@ -1,5 +1,7 @@
 // A decoder model built from a plan: embedding, layers run in the plan's order, final norm, head.
 // Nothing here names an architecture; the plan says which parts and which order.
+#include <cstdio>
+
 #include "ops.h"
 
 namespace vmb {
@@ -8,6 +10,18 @@ namespace vmb {
 void* StepContext::take_tokens(long long cols, DType dtype) { return ws->take(static_cast<size_t>(T_cap) * cols * dtype_size(dtype)); }
 
 void* StepContext::take(long long elements, DType dtype) { return ws->take(static_cast<size_t>(elements) * dtype_size(dtype)); }
+
+void* StepContext::share(const std::string& name, long long cols, DType dtype) {
+    if (shared_buffers.count(name)) throw Error("a step buffer named '" + name + "' is shared twice");
+    Shared s{take_tokens(cols, dtype), cols, dtype};
+    shared_buffers[name] = s;
+    return s.ptr;
+}
+
+const StepContext::Shared* StepContext::shared(const std::string& name) const {
+    auto it = shared_buffers.find(name);
+    return it == shared_buffers.end() ? nullptr : &it->second;
+}
 
 KVView StepContext::kv() const {
     const std::pair<int, int> where = cache->book.where(run);
@@ -128,6 +142,8 @@ void DecoderModel::forward(StepContext& ctx) {
         ctx.give(rows);
     }
     ctx.give(pending);
+    for (auto& kv : ctx.shared_buffers) ctx.give(kv.second.ptr);      // what runs left for later runs of this step
+    ctx.shared_buffers.clear();
     ctx.give(h);
 }
 
@@ -137,9 +153,25 @@ std::shared_ptr<DecoderModel> load_model(const std::string& folder, DType dtype,
     const json::Value data = read_config_json(folder);
     const std::string where = folder + "/config.json";
     const PlanFunction plan_of = resolve_architecture(data, where);
-    auto model = std::make_shared<DecoderModel>(plan_of(data, where));
+    // A size that config.json leaves to the checkpoint (the rows of a table) is read from the tensors' shapes: the plan function
+    // finds them under the key `tensor_shapes`, name -> list of extents.
+    const std::string path = folder + "/model.safetensors";
+    HostTensors found;
+    json::Value with_shapes = data;
+    if (FILE* f = std::fopen(path.c_str(), "rb")) {
+        std::fclose(f);
+        found = load_safetensors(path);
+        json::Value shapes;
+        for (const auto& kv : found) {
+            json::Array extents;
+            for (long long d : kv.second.shape) extents.emplace_back(d);
+            shapes.set(kv.first, json::Value(extents));
+        }
+        if (!found.empty()) with_shapes.set("tensor_shapes", shapes);
+    }
+    auto model = std::make_shared<DecoderModel>(plan_of(with_shapes, where));
     model->config = data;
-    const HostTensors tensors = load_weights(folder, model->weight_table());
+    const HostTensors tensors = found.empty() ? load_weights(folder, model->weight_table()) : check_and_bind(found, model->weight_table(), path);
     const int dev = require_cuda(device);          // one clear refusal before the first tensor moves: there is no CPU fallback
     cudaStream_t stream = nullptr;
     ops::cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "creating a stream");

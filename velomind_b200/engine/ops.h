@@ -149,6 +149,80 @@ inline void experts_few_tokens(const void* x, const float* norm_w, float eps, co
     ++counters().own_launches;          // two kernels
 }
 
+// the general forms: a router that scores all outputs, gated experts, identity experts (csrc/routed_experts.cu)
+struct ExpertKind {
+    int E = 0, n_identity = 0;          // real experts; identity experts behind them in the router's outputs
+    int act_kind = VM_ACT_RELU_SQUARED;
+    bool glu = false;                   // gated experts with the clamped unit
+    float limit = 0.f, alpha = 0.f;
+};
+
+inline void expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                                 int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, DType act,
+                                 cudaStream_t s) {
+    Timed t("expert_router", s);
+    check(vm_expert_router_scored(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, scale, chosen, weight, code(act), s),
+          "expert_router", s);
+}
+
+inline void experts_few_tokens_glu(const void* x, const float* norm_w, float eps, const DeviceTensor& up, const DeviceTensor& down, const void* up_shared,
+                                   const void* down_shared, const int* chosen, const float* weight, const float* shared_gate, int T, int hidden, int ff,
+                                   int ff_shared, int top, int act_kind_shared, const ExpertKind& k, void* act, void* out, float* residual,
+                                   DType act_dtype, cudaStream_t s) {
+    Timed t("experts_few_tokens", s);
+    check(vm_experts_few_tokens_glu(x, norm_w, eps, up.ptr, down.ptr, up_shared, down_shared, code(up.dtype), chosen, weight, shared_gate, T, hidden, ff,
+                                    ff_shared, top, k.act_kind, act_kind_shared, k.E, k.n_identity, k.glu ? 1 : 0, k.limit, k.alpha, act, out, residual,
+                                    code(act_dtype), s),
+          "experts_few_tokens", s);
+    ++counters().own_launches;          // two kernels
+}
+
+inline void experts_grouped_glu(const void* x, const DeviceTensor& up, const DeviceTensor& down, const int* chosen, const float* weight,
+                                const float* shared_y, const float* shared_gate, int T, int hidden, int ff, int top, const ExpertKind& k, int row_cap,
+                                int* row_of_pair, int* token_of_row, int* expert_of_tile, void* x_sorted, void* act, void* gate_up, float* y, void* out,
+                                int* err, cudaStream_t s) {
+    Timed t(x_sorted ? "experts_grouped_tc" : "experts_grouped", s);
+    check(vm_experts_grouped_glu(x, up.ptr, down.ptr, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, k.E, k.n_identity, k.act_kind,
+                                 k.glu ? 1 : 0, k.limit, k.alpha, row_cap, row_of_pair, token_of_row, expert_of_tile, x_sorted, act, gate_up, y, out, err, s),
+          "experts_grouped", s);
+    counters().own_launches += (x_sorted ? 4 : 3) + (k.glu ? 1 : 0);
+}
+
+inline void qkv_prepare(void* qkv, int ld, const float* wq, const float* wk, float eps, const float* lambda, const void* v_first, void* v_keep,
+                        const StepContext& ctx, const KVView& kv, int H, int Hkv, int Dk, int Dv) {
+    Timed t("qkv_prepare", ctx.stream);
+    check(vm_qkv_prepare(qkv, ld, wq, wk, eps, lambda, v_first, v_keep, ctx.positions, ctx.seq_of_token, kv.block_table, kv.table_width,
+                         kv.owns ? kv.k_pages : nullptr, kv.owns ? kv.v_pages : nullptr, ctx.T, H, Hkv, Dk, Dv, kv.owns ? kv.n_pages : 0,
+                         code(ctx.act_dtype), ctx.err, ctx.stream),
+          "qkv_prepare", ctx.stream);
+}
+
+// what the biased attention kernels need beside the sizes: the bias table, the distance table, the mask
+struct BiasedMask {
+    const float* rel = nullptr;         // device float32 [rows, H], or null: no bias
+    const int* bucket_of = nullptr;     // device int32 [far + 1]
+    int far = 0, window = 0, keep_first = 0;
+};
+// attention of the step's tokens over the cache with that mask and bias; keys of Dk, values of Dv; picks the kernel by shape and dtype
+void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int Dk, int Dv, float scale,
+                      const BiasedMask& mask);
+
+// the state-space mixer's kernels over the running schedule position's state area
+inline void ssm_mixer(const void* proj, int ld, const float* taps, const float* conv_bias, const float* dt_bias, const float* A_log, const float* Dskip,
+                      const float* norm_w, float eps, StepContext& ctx, void* out, int H, int P, int N, int G, int K, int parts) {
+    Timed t("ssm_mixer", ctx.stream);
+    if (!ctx.state() || ctx.state_floats() < vm_ssm_state_floats(H, P, N, G, K)) throw CacheError("ssm: the cache holds no state area of this layer's size");
+    const long long C = static_cast<long long>(H) * P + 2ll * G * N;
+    void* xbc = ctx.take_tokens(C, ctx.act_dtype);
+    float* y = static_cast<float*>(ctx.take_tokens(static_cast<long long>(H) * P, DType::F32));
+    check(vm_ssm_mixer(proj, ld, taps, conv_bias, dt_bias, A_log, Dskip, norm_w, eps, ctx.state(), ctx.state_floats(), ctx.positions, ctx.seq_of_token,
+                       ctx.cu_tokens, ctx.slots, xbc, y, out, ctx.T, ctx.B, H, P, N, G, K, parts, code(ctx.act_dtype), ctx.stream),
+          "ssm_mixer", ctx.stream);
+    counters().own_launches += K > 1 ? 3 : 2;      // four kernels
+    ctx.give(y);
+    ctx.give(xbc);
+}
+
 inline void activation(const void* in, void* out, long long n, int kind, DType act, cudaStream_t s) {
     Timed t("activation", s);
     check(vm_activation(in, out, n, kind, code(act), s), "activation", s);

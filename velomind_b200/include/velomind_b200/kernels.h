@@ -74,6 +74,41 @@ int vm_experts_few_tokens(const void* x, const float* norm_w, float eps, const v
                           int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, void* act, void* out,
                           float* residual, int act_dtype, cudaStream_t stream);
 
+// the same with gated experts and identity experts: E real experts; a chosen index >= E names one of the n_identity identity experts,
+// whose result is the token's input row; glu: an expert's up matrix is [2 * ff, hidden] (gate rows first) and its activation
+// min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1); act [T, vm_experts_act_cols(...)]
+long long vm_experts_act_cols(int hidden, int ff, int ff_shared, int top, int n_identity);
+int vm_experts_few_tokens_glu(const void* x, const float* norm_w, float eps, const void* w_up, const void* w_down, const void* w_up_shared,
+                              const void* w_down_shared, int weight_dtype, const int* chosen, const float* weight, const float* shared_gate, int T,
+                              int hidden, int ff, int ff_shared, int top, int act_kind, int act_kind_shared, int E, int n_identity, int glu,
+                              float limit, float alpha, void* act, void* out, float* residual, int act_dtype, cudaStream_t stream);
+// a router that scores all its n_out outputs: s = softmax(z); the choice goes by s + correction (null: none) among the outputs of the
+// group_keep best of group_count equal groups of neighbours (a group's score: its largest choice score); weight = s * scale
+int vm_expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                            int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, int act_dtype,
+                            cudaStream_t stream);
+
+// ---- attention_biased.cu: windowed attention with kept first tokens and a learned bias by bucketed distance; keys of Dk, values of Dv
+// qkv [T, ld]: H query heads and Hkv key heads of Dk, Hkv value heads of Dv; queries and keys get a unit-rms norm per head (weights wq, wk
+// float32 [Dk]), queries in place, keys and values into the pages (kpages null: none written); v_first [T, Hkv * Dv] is blended into the
+// values with the device float `lambda` ((1 - lambda) v + lambda v_first); v_keep [T, Hkv * Dv] receives the values as projected
+int vm_qkv_prepare(void* qkv, int ld, const float* wq, const float* wk, float eps, const float* lambda, const void* v_first, void* v_keep,
+                   const int* positions, const int* seq_of_token, const int* block_table, int max_blocks, void* kpages, void* vpages, int T, int H,
+                   int Hkv, int Dk, int Dv, int n_pages, int act_dtype, int* err, cudaStream_t stream);
+// rel float32 [rows, H], bucket_of int32 [far + 1] (distances beyond `far` read the last entry); both null: no bias.
+// A query at position p sees keys j <= p with p - j < window (0: all) or j < keep_first.
+int vm_attention_biased_generic(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
+                                const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, void* out,
+                                int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int act_dtype,
+                                int* err, cudaStream_t stream);
+
+// ---- ssm.cu: a selective state-space mixer (short causal convolution, matrix-state recurrence, gated group norm)
+long long vm_ssm_state_floats(int H, int P, int N, int G, int K);
+int vm_ssm_mixer(const void* proj, int ld, const float* taps, const float* conv_bias, const float* dt_bias, const float* A_log, const float* Dskip,
+                 const float* norm_w, float eps, float* state, int state_floats, const int* positions, const int* seq_of_token, const int* cu_tokens,
+                 const int* slots, void* xbc, float* y, void* out, int T, int B, int H, int P, int N, int G, int K, int parts, int act_dtype,
+                 cudaStream_t stream);
+
 // ---- rope_cache.cu
 int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
                      const float* inv_freq, int rot_dim, int pairing, void* kpages, void* vpages, int T, int H, int Hkv, int D,
@@ -105,6 +140,12 @@ int vm_experts_grouped(const void* x, const void* w_up, const void* w_down, cons
                        const float* shared_gate, int T, int hidden, int ff, int top, int E, int act_kind, int row_cap, int* row_of_pair,
                        int* token_of_row, int* expert_of_tile, void* act, float* y, void* out, cudaStream_t stream);
 int vm_activation(const void* in, void* out, long long n, int kind, int act_dtype, cudaStream_t stream);
+// the general form: gated and identity experts as in vm_experts_few_tokens_glu; x_sorted given: tcgen05 tiles of 128 rows, else mma.sync
+// tiles of 64; gate_up bf16 [row_cap, 2 * ff] is scratch of the gated form
+int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,
+                           const float* shared_gate, int T, int hidden, int ff, int top, int E, int n_identity, int act_kind, int glu, float limit,
+                           float alpha, int row_cap, int* row_of_pair, int* token_of_row, int* expert_of_tile, void* x_sorted, void* act,
+                           void* gate_up, float* y, void* out, int* err, cudaStream_t stream);
 // the same with the experts' products on tcgen05: runs padded to tiles of 128 rows, x_sorted bf16 [row_cap, hidden] as one more scratch
 long long vm_experts_grouped_rows_tiled(int T, int top, int E, int tile);
 int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* chosen, const float* weight, const float* shared_y,

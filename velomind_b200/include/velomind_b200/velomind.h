@@ -275,6 +275,7 @@ public:
     DeviceTensor upload(const HostTensor& t, DType as);
     DeviceTensor upload_stacked(const std::vector<const HostTensor*>& parts, DType as);   // rows of several matrices, one tensor
     DeviceTensor upload_floats(const std::vector<float>& values);
+    DeviceTensor upload_ints(const std::vector<int>& values);
     // dtype a weight matrix is kept in: the compute dtype, except that a tensor stored in 32-bit stays 32-bit
     DType matrix_dtype(const std::vector<const HostTensor*>& stored) const;
 
@@ -308,11 +309,13 @@ private:
 struct CacheNeed {
     enum Kind { None, All, Window } kind = None;   // every earlier key/value; the last `window`; nothing
     int kv_heads = 0;
-    int key_dim = 0, value_dim = 0;                // per head; the paged storage wants them equal, or value_dim 0: one row per token only
+    int key_dim = 0, value_dim = 0;                // per head; they may differ; value_dim 0: one row per token only
     int window = 0;
+    int keep_first = 0;                            // a window group keeps the pages of the first `keep_first` tokens for good
     int state_floats = 0;                          // fixed-size float32 state per sequence (0: none)
     bool same_group(const CacheNeed& o) const {
-        return kind == o.kind && kv_heads == o.kv_heads && key_dim == o.key_dim && value_dim == o.value_dim && window == o.window;
+        return kind == o.kind && kv_heads == o.kv_heads && key_dim == o.key_dim && value_dim == o.value_dim && window == o.window &&
+               keep_first == o.keep_first;
     }
 };
 
@@ -328,7 +331,11 @@ public:
     CacheNeed need;
     int n_pages, max_slots, max_blocks;
     FreeList pages;
-    std::vector<int> blocks_begin, blocks_end;     // logical blocks [begin, end) of a slot hold a page
+    std::vector<int> blocks_begin, blocks_end;     // logical blocks [begin, end) of a slot hold a page, and so do the kept first ones
+    int kept_blocks() const;                       // blocks at the start of a sequence that a window group never gives back
+    bool holds(int slot, int block) const {        // whether that logical block of the slot has a page
+        return block < blocks_end[slot] && (block >= blocks_begin[slot] || block < kept_blocks());
+    }
     uint64_t version = 0;                          // grows whenever an entry of the block table changes
 
 private:
@@ -361,7 +368,7 @@ private:
     std::vector<std::pair<int, int>> where_;
 };
 
-// The book plus the device storage: k/v[layer, page, kv_head, VM_PAGE_TOKENS, head_dim] per group, and a float32 state area
+// The book plus the device storage: k[layer, page, kv_head, VM_PAGE_TOKENS, key_dim] and v[..., value_dim] per group, and a float32 state area
 // [max_slots, n] for every run that asks for one (zeroed when a slot is opened).  Keys are stored after the position
 // encoding, as the reference caches them (examples/common/llama/llama_graph.cpp:210-215).
 class SequenceCache {
@@ -372,7 +379,7 @@ public:
     void close(int slot) { book.close(slot); }
     CacheBook book;
     DType dtype;
-    struct GroupStorage { std::unique_ptr<DeviceBuffer> k, v; size_t layer_bytes = 0; };
+    struct GroupStorage { std::unique_ptr<DeviceBuffer> k, v; size_t layer_bytes = 0, value_layer_bytes = 0; };
     std::vector<GroupStorage> storage;
     std::vector<std::shared_ptr<DeviceBuffer>> state;   // per schedule position (null: none)
     void* k_pages(int group, int layer) const;
@@ -434,8 +441,8 @@ struct RotaryTable {                            // what a position encoding hand
 };
 
 struct KVView {
-    void* k_pages = nullptr;                    // [n_pages, kv_heads, VM_PAGE_TOKENS, head_dim]
-    void* v_pages = nullptr;                    // null for a group that keeps one row per token
+    void* k_pages = nullptr;                    // [n_pages, kv_heads, VM_PAGE_TOKENS, key_dim]
+    void* v_pages = nullptr;                    // [..., value_dim]; null for a group that keeps one row per token
     const int* block_table = nullptr;           // device int32 [B, table_width]
     int table_width = 0, n_pages = 0;
     bool owns = true;                           // false: the run reads another run's cache and must not write it
@@ -469,6 +476,12 @@ struct StepContext {
     void* take_tokens(long long cols, DType dtype);     // [T, cols], backed by T_cap rows so that a bucket's plan fits every step
     void* take(long long elements, DType dtype);
     void give(void* p) { ws->give(p); }
+    // Buffers that one run leaves for later runs of the same step (the values of a first layer that later layers blend in):
+    // `share` takes [T_cap, cols] under a name, `shared` finds it (null: none); the model gives them back when the step ends.
+    struct Shared { void* ptr = nullptr; long long cols = 0; DType dtype = DType::F32; };
+    std::map<std::string, Shared> shared_buffers;
+    void* share(const std::string& name, long long cols, DType dtype);
+    const Shared* shared(const std::string& name) const;
     KVView kv() const;                          // the cache of the running schedule position
     float* state() const;                       // its float32 state [max_slots, n] (index with `slots`), or null
     int state_floats() const;

@@ -98,6 +98,73 @@ private:
 
 int activation_code(const std::string& name, const char* part);     // parts/routed_experts.cpp
 
+// The two-matrix unit without a gate: down(act(up(x))), no biases; `activation` and the tensors' names are arguments.
+class PlainMLP : public FeedForward {
+public:
+    PlainMLP(int hidden, int intermediate, int activation, std::string up, std::string down)
+        : hidden_(hidden), I_(intermediate), act_(activation), up_name_(std::move(up)), down_name_(std::move(down)) {}
+
+    WeightTable weight_specs() const override {
+        WeightTable t;
+        t[up_name_].shape = {I_, hidden_};
+        t[down_name_].shape = {hidden_, I_};
+        return t;
+    }
+
+    void bind(const Weights& w, BindContext& bc) override {
+        up_.bind({&w.at(up_name_)}, bc);
+        down_.bind({&w.at(down_name_)}, bc);
+    }
+
+    bool graph_safe() const override { return true; }
+
+    int max_rows() const { return ops::skinny_max_rows(2 * up_.weight.rows() * up_.weight.cols()); }
+
+    bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
+        const float* nw;
+        float eps;
+        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
+        if (up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
+        if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && I_ % 32 == 0;
+        return hidden_ % 8 == 0 && I_ % 8 == 0;
+    }
+
+    // h += down(act(up(norm(h)))): the norm in the first product (few tokens), the sum in the second
+    void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
+        const float* nw = nullptr;
+        float eps = 0.f;
+        norm.as_rms(&nw, &eps);
+        const bool skinny = ctx.T_cap <= max_rows();
+        void* u = ctx.take_tokens(I_, DType::BF16);
+        if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
+            ops::skinny_linear(h, nw, eps, up_.weight, ctx.T, u, I_, false, nullptr, ctx.err, ctx.stream);
+        } else {
+            void* x = ctx.take_tokens(hidden_, DType::BF16);
+            norm.forward(ctx, h, nullptr, x, nullptr, 0);
+            if (skinny) ops::skinny_linear(x, nullptr, 0.f, up_.weight, ctx.T, u, I_, false, nullptr, ctx.err, ctx.stream);
+            else ops::linear(x, DType::BF16, hidden_, up_.weight, u, DType::BF16, ctx.T, ctx.stream);
+            ctx.give(x);
+        }
+        ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, DType::BF16, ctx.stream);
+        if (skinny) ops::skinny_linear(u, nullptr, 0.f, down_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
+        else ops::linear_residual(u, I_, down_.weight, h, ctx.T, ctx.stream);
+        ctx.give(u);
+    }
+
+    void forward(StepContext& ctx, const void* x, void* out) override {
+        void* u = ctx.take_tokens(I_, ctx.act_dtype);
+        up_.apply(ctx, x, ctx.act_dtype, u, ctx.act_dtype, ctx.T, ctx.T_cap);
+        ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, ctx.act_dtype, ctx.stream);
+        down_.apply(ctx, u, ctx.act_dtype, out, ctx.act_dtype, ctx.T, ctx.T_cap);
+        ctx.give(u);
+    }
+
+private:
+    int hidden_, I_, act_;
+    std::string up_name_, down_name_;
+    Linear up_, down_;
+};
+
 namespace {
 RegisterPart reg("feed_forward", "swiglu", [](const json::Value& a) {
     return std::make_shared<SwiGLU>(static_cast<int>(arg_int(a, "hidden", "swiglu")), static_cast<int>(arg_int(a, "intermediate", "swiglu")));
@@ -108,6 +175,13 @@ RegisterPart reg_gated("feed_forward", "gated", [](const json::Value& a) {
     return std::make_shared<SwiGLU>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "intermediate", k)),
                                     activation_code(arg_string_or(a, "activation", "silu", k), k), arg_string_or(a, "gate", "gate_proj.weight", k),
                                     arg_string_or(a, "up", "up_proj.weight", k), arg_string_or(a, "down", "down_proj.weight", k));
+});
+// the unit without a gate
+RegisterPart reg_mlp("feed_forward", "mlp", [](const json::Value& a) {
+    const char* k = "mlp";
+    return std::make_shared<PlainMLP>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "intermediate", k)),
+                                      activation_code(arg_string_or(a, "activation", "relu_squared", k), k), arg_string_or(a, "up", "up", k),
+                                      arg_string_or(a, "down", "down", k));
 });
 }  // namespace
 

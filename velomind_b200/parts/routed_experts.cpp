@@ -6,6 +6,12 @@
 //
 // Experts are two-layer networks without biases; `activation` names theirs (the shared expert may have another).  The router,
 // its bias and the shared gate stay float32 on the device whatever the compute dtype.
+//
+// A second form of routing (`routing` = "scored"): s = softmax(z) over ALL the router's outputs; the choice goes by s plus a
+// stored correction (tensor `correction`), which steers the choice but not the weights, among the outputs of the `groups_keep`
+// best of `groups` equal groups of neighbours (a group's score is its largest choice score); the weights are s * `scale`, not
+// renormalised.  The last `identity` outputs of the router are identity experts without tensors: their result is the input.
+// A second form of expert (`glu` = 1): gate and up matrices, min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) + 1).
 #include "args.h"
 #include "linear.h"
 
@@ -18,18 +24,49 @@ int activation_code(const std::string& name, const char* part) {
     throw ConfigError(format("part '%s': activation '%s' is not known (silu, gelu_tanh, relu_squared)", part, name.c_str()));
 }
 
+// how the router turns its outputs into chosen experts and weights
+struct Routing {
+    bool scored = false;                 // false: softmax over the chosen logits; true: the form described above
+    int groups = 1, groups_keep = 1, identity = 0;
+    float scale = 1.f;
+    bool glu = false;
+    float limit = 0.f, alpha = 1.702f;
+};
+
 class RoutedExperts : public FeedForward {
 public:
-    RoutedExperts(int hidden, int experts, int top, int ff, int act, int shared_ff, int shared_act, bool shared_gate)
-        : hidden_(hidden), E_(experts), top_(top), ff_(ff), act_(act), sff_(shared_ff), sact_(shared_act), gate_(shared_gate && shared_ff > 0) {
-        if (top < 1 || top > experts) throw ConfigError(format("part 'routed_experts': top (%d) must be within 1..experts (%d)", top, experts));
+    RoutedExperts(int hidden, int experts, int top, int ff, int act, int shared_ff, int shared_act, bool shared_gate, const Routing& r = {})
+        : hidden_(hidden), E_(experts), top_(top), ff_(ff), act_(act), sff_(shared_ff), sact_(shared_act), gate_(shared_gate && shared_ff > 0), r_(r) {
+        const char* k = "routed_experts";
+        if (experts < 1 || r.identity < 0) throw ConfigError(format("part '%s': experts must be positive and identity not negative", k));
+        const int outputs = experts + r.identity;
+        if (!r.scored && (r.identity > 0 || r.groups != 1)) throw ConfigError(format("part '%s': identity experts and groups belong to routing \"scored\"", k));
+        if (r.groups < 1 || outputs % r.groups || r.groups_keep < 1 || r.groups_keep > r.groups)
+            throw ConfigError(format("part '%s': %d groups (of which %d stay) must divide the router's %d outputs", k, r.groups, r.groups_keep, outputs));
+        const int eligible = outputs / r.groups * r.groups_keep;
+        if (top < 1 || top > eligible) throw ConfigError(format("part '%s': top (%d) must be within 1..%d, the outputs that can be chosen", k, top, eligible));
+        if (r.glu && !(r.limit > 0)) throw ConfigError(format("part '%s': gated experts need a positive limit", k));
     }
+
+    ops::ExpertKind kind() const {
+        ops::ExpertKind k;
+        k.E = E_;
+        k.n_identity = r_.identity;
+        k.act_kind = act_;
+        k.glu = r_.glu;
+        k.limit = r_.limit;
+        k.alpha = r_.alpha;
+        return k;
+    }
+    bool general() const { return r_.scored || r_.glu; }      // the steps that take the general kernels
 
     WeightTable weight_specs() const override {
         WeightTable t;
-        t["router"].shape = {E_, hidden_};
-        t["router.b"].shape = {E_};
+        t["router"].shape = {E_ + r_.identity, hidden_};
+        if (r_.scored) t["correction"].shape = {E_ + r_.identity};
+        else t["router.b"].shape = {E_};
         for (int e = 0; e < E_; ++e) {
+            if (r_.glu) t[format("e%d.gate", e)].shape = {ff_, hidden_};
             t[format("e%d.up", e)].shape = {ff_, hidden_};
             t[format("e%d.down", e)].shape = {hidden_, ff_};
         }
@@ -43,9 +80,10 @@ public:
 
     void bind(const Weights& w, BindContext& bc) override {
         router_ = bc.upload(w.at("router"), DType::F32);
-        router_b_ = bc.upload(w.at("router.b"), DType::F32);
+        router_b_ = bc.upload(w.at(r_.scored ? "correction" : "router.b"), DType::F32);
         std::vector<const HostTensor*> ups, downs, all;
         for (int e = 0; e < E_; ++e) {
+            if (r_.glu) ups.push_back(&w.at(format("e%d.gate", e)));      // an expert's gate rows lie before its up rows
             ups.push_back(&w.at(format("e%d.up", e)));
             downs.push_back(&w.at(format("e%d.down", e)));
         }
@@ -88,17 +126,32 @@ public:
         run_few(ctx, h, nw, eps, nullptr, h);
     }
 
+    // chosen experts and weights of every token (and the shared expert's gate), by the part's form of routing
+    void route(StepContext& ctx, const void* x, const float* nw, float eps, int* chosen, float* weight, float* sgate) {
+        if (r_.scored) {
+            if (gate_) throw Error("routed_experts: the scored router has no gate for a shared expert");
+            ops::expert_router_scored(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr), ctx.T, hidden_,
+                                      E_ + r_.identity, top_, r_.groups, r_.groups_keep, r_.scale, chosen, weight, ctx.act_dtype, ctx.stream);
+            return;
+        }
+        ops::expert_router(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
+                           gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
+                           ctx.stream);
+    }
+
     // the few-token path: x in the activation dtype, or (nw given) the float32 residual stream; `residual` given: added into
     void run_few(StepContext& ctx, const void* x, const float* nw, float eps, void* out, float* residual) {
         int* chosen = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
         float* weight = static_cast<float*>(ctx.take_tokens(top_, DType::F32));
         float* sgate = gate_ ? static_cast<float*>(ctx.take_tokens(1, DType::F32)) : nullptr;
-        ops::expert_router(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
-                           gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
-                           ctx.stream);
-        void* act = ctx.take_tokens(static_cast<long long>(top_) * ff_ + sff_, ctx.act_dtype);
-        ops::experts_few_tokens(x, nw, eps, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T,
-                                hidden_, ff_, sff_, top_, act_, sact_, act, out, residual, ctx.act_dtype, ctx.stream);
+        route(ctx, x, nw, eps, chosen, weight, sgate);
+        void* act = ctx.take_tokens(vm_experts_act_cols(hidden_, ff_, sff_, top_, r_.identity), ctx.act_dtype);
+        if (general())
+            ops::experts_few_tokens_glu(x, nw, eps, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate,
+                                        ctx.T, hidden_, ff_, sff_, top_, sact_, kind(), act, out, residual, ctx.act_dtype, ctx.stream);
+        else
+            ops::experts_few_tokens(x, nw, eps, up_, down_, sff_ > 0 ? s_up_.ptr : nullptr, sff_ > 0 ? s_down_.ptr : nullptr, chosen, weight, sgate, ctx.T,
+                                    hidden_, ff_, sff_, top_, act_, sact_, act, out, residual, ctx.act_dtype, ctx.stream);
         ctx.give(act);
         ctx.give(sgate);
         ctx.give(weight);
@@ -113,9 +166,7 @@ public:
         int* chosen = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
         float* weight = static_cast<float*>(ctx.take_tokens(top_, DType::F32));
         float* sgate = gate_ ? static_cast<float*>(ctx.take_tokens(1, DType::F32)) : nullptr;
-        ops::expert_router(x, nullptr, 0.f, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
-                           gate_ ? static_cast<const float*>(s_gate_.ptr) : nullptr, ctx.T, hidden_, E_, top_, chosen, weight, sgate, ctx.act_dtype,
-                           ctx.stream);
+        route(ctx, x, nullptr, 0.f, chosen, weight, sgate);
         // Many tokens (by the step's capacity, so that a bucket's steps ask for the same scratch): pairs grouped by expert, tensor-core
         // tiles per expert, the shared expert as two library products.  Few tokens: every token streams the rows of its experts.
         {
@@ -129,14 +180,21 @@ public:
                 ctx.give(u);
             }
             // the experts' tiles on tcgen05 from TC_FROM_TOKENS on (tiles of 128 rows, rows gathered first), on mma.sync below
-            const bool tc = ctx.T_cap >= TC_FROM_TOKENS && ctx.err != nullptr;
+            const bool tc = ctx.T_cap >= TC_FROM_TOKENS && ctx.err != nullptr && (!general() || (ff_ % 64 == 0 && hidden_ % 64 == 0));
             const int row_cap = static_cast<int>(tc ? vm_experts_grouped_rows_tiled(ctx.T_cap, top_, E_, 128) : vm_experts_grouped_rows(ctx.T_cap, top_, E_));
             int* row_of_pair = static_cast<int*>(ctx.take_tokens(top_, DType::I32));
             int* token_of_row = static_cast<int*>(ctx.take(row_cap, DType::I32));
             int* expert_of_tile = static_cast<int*>(ctx.take(row_cap / 64, DType::I32));
             void* act = ctx.take(static_cast<long long>(row_cap) * ff_, DType::BF16);
             float* y = static_cast<float*>(ctx.take(static_cast<long long>(row_cap) * hidden_, DType::F32));
-            if (tc) {
+            if (general()) {
+                void* gate_up = r_.glu ? ctx.take(2ll * row_cap * ff_, DType::BF16) : nullptr;
+                void* x_sorted = tc ? ctx.take(static_cast<long long>(row_cap) * hidden_, DType::BF16) : nullptr;
+                ops::experts_grouped_glu(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, kind(), row_cap, row_of_pair,
+                                         token_of_row, expert_of_tile, x_sorted, act, gate_up, y, out, ctx.err, ctx.stream);
+                ctx.give(x_sorted);
+                ctx.give(gate_up);
+            } else if (tc) {
                 void* x_sorted = ctx.take(static_cast<long long>(row_cap) * hidden_, DType::BF16);
                 ops::experts_grouped_tc(x, up_, down_, chosen, weight, shared_y, sgate, ctx.T, hidden_, ff_, top_, E_, act_, row_cap, row_of_pair,
                                         token_of_row, expert_of_tile, x_sorted, act, y, out, ctx.err, ctx.stream);
@@ -164,6 +222,7 @@ public:
 private:
     int hidden_, E_, top_, ff_, act_, sff_, sact_;
     bool gate_;
+    Routing r_;
     DeviceTensor router_, router_b_, up_, down_, s_up_, s_down_, s_gate_;
 };
 
@@ -171,10 +230,21 @@ namespace {
 RegisterPart reg("feed_forward", "routed_experts", [](const json::Value& a) {
     const char* k = "routed_experts";
     const std::string act = arg_string_or(a, "activation", "relu_squared", k);
+    Routing r;
+    const std::string routing = arg_string_or(a, "routing", "chosen_softmax", k);
+    if (routing != "chosen_softmax" && routing != "scored") throw ConfigError("part 'routed_experts': routing is \"chosen_softmax\" or \"scored\"");
+    r.scored = routing == "scored";
+    r.groups = static_cast<int>(arg_int_or(a, "groups", 1, k));
+    r.groups_keep = static_cast<int>(arg_int_or(a, "groups_keep", r.groups, k));
+    r.identity = static_cast<int>(arg_int_or(a, "identity", 0, k));
+    r.scale = static_cast<float>(arg_number_or(a, "scale", 1.0, k));
+    r.glu = arg_int_or(a, "glu", 0, k) != 0;
+    r.limit = static_cast<float>(arg_number_or(a, "limit", 0.0, k));
+    r.alpha = static_cast<float>(arg_number_or(a, "alpha", 1.702, k));
     return std::make_shared<RoutedExperts>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "experts", k)),
                                            static_cast<int>(arg_int(a, "top", k)), static_cast<int>(arg_int(a, "ff", k)), activation_code(act, k),
                                            static_cast<int>(arg_int_or(a, "shared_ff", 0, k)),
-                                           activation_code(arg_string_or(a, "shared_activation", act, k), k), arg_int_or(a, "shared_gate", 1, k) != 0);
+                                           activation_code(arg_string_or(a, "shared_activation", act, k), k), arg_int_or(a, "shared_gate", 1, k) != 0, r);
 });
 }  // namespace
 
