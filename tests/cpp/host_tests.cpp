@@ -139,9 +139,14 @@ TEST(groups_with_different_needs_have_their_own_storage) {
     c.check();
     c.close(s);
     c.check();
+    // keys and values of unequal sizes share a group only with their like
     CacheNeed unequal = all_keys(2, 16);
     unequal.value_dim = 32;
-    THROWS(CacheError, "keys of 16 and values of 32", CacheBook({unequal}, {-1}, 64 * 4, 256));
+    CacheBook two({unequal, all_keys(2, 16), unequal}, {-1, -1, -1}, 64 * 4, 256);
+    CHECK(two.groups.size() == 2 && two.where(0) == std::make_pair(0, 0) && two.where(2) == std::make_pair(0, 1) && two.where(1).first == 1);
+    CacheNeed no_key = all_keys(2, 16);
+    no_key.key_dim = 0;
+    THROWS(CacheError, "keys of a positive size", CacheBook({no_key}, {-1}, 64 * 4, 256));
     // one row per token and no second one (a latent that is key and value at once) is a group like any other; a run that keeps
     // only a fixed-size state has none; a run may read another run's rows
     CacheNeed latent = all_keys(1, 48);
@@ -158,6 +163,46 @@ TEST(groups_with_different_needs_have_their_own_storage) {
     CHECK(no_keys.groups.empty() && no_keys.tokens_held() == 0 && no_keys.length[only] == 200);
     no_keys.close(only);
     no_keys.check();
+}
+
+TEST(a_window_group_keeps_the_pages_of_its_first_tokens) {
+    CacheNeed win;
+    win.kind = CacheNeed::Window;
+    win.kv_heads = 1;
+    win.key_dim = 32;
+    win.value_dim = 16;
+    win.window = 70;
+    win.keep_first = 65;                               // two pages stay for good
+    CacheNeed plain_window = win;
+    plain_window.keep_first = 0;
+    CacheBook c({win, plain_window}, {-1, -1}, 64 * 12, 4096);
+    CHECK(c.groups.size() == 2 && c.groups[0].kept_blocks() == 2 && c.groups[1].kept_blocks() == 0);
+    const int s = c.open();
+    c.reserve(s, 500);
+    c.commit(s, 500);
+    // the next query (position 500) sees keys 431..500: blocks 6 and 7, and with kept first tokens blocks 0 and 1 as well
+    CHECK(c.groups[0].pages.held_count() == 4 && c.groups[1].pages.held_count() == 2);
+    CHECK(c.groups[0].holds(s, 0) && c.groups[0].holds(s, 1) && !c.groups[0].holds(s, 2) && !c.groups[0].holds(s, 5) && c.groups[0].holds(s, 6));
+    CHECK(c.groups[0].table_row(s)[1] >= 0 && c.groups[0].table_row(s)[3] == -1 && c.groups[1].table_row(s)[0] == -1);
+    c.check();
+    // decoding on: a page more, the oldest of the window goes, the first two stay
+    c.reserve(s, 600);
+    c.commit(s, 600);
+    CHECK(c.groups[0].holds(s, 1) && !c.groups[0].holds(s, 7) && c.groups[0].holds(s, 8) && c.groups[0].holds(s, 9));
+    c.check();
+    const int other = c.open();
+    c.reserve(other, 30);                              // shorter than what is kept: nothing to give back, nothing lost
+    c.commit(other, 30);
+    CHECK(c.groups[0].holds(other, 0) && c.groups[0].pages.held_count() == 5);
+    c.close(s);
+    c.check();
+    CHECK(c.groups[0].pages.held_count() == 1);
+    c.close(other);
+    c.check();
+    CHECK(c.groups[0].pages.held_count() == 0 && c.groups[1].pages.held_count() == 0);
+    CacheNeed bad = all_keys(1, 16);
+    bad.keep_first = 4;
+    THROWS(CacheError, "keep_first", CacheBook({bad}, {-1}, 64 * 4, 256));
 }
 
 // ------------------------------------------------------------------------------------------------ arena

@@ -79,8 +79,8 @@ def attention(x, w, p, m, eps, v_first=None, return_weights=False):
     if v_first is not None:
         lam = float(np.asarray(w[p + "vmix"], D64).reshape(()))
         v = (1.0 - lam) * v + lam * v_first
-    rel = np.asarray(w[p + "rel"], D64)
-    rows = rel.shape[0]
+    rel = np.asarray(w[p + "rel"], D64) if p + "rel" in w else None      # (a part without a table: no bias)
+    rows = rel.shape[0] if rel is not None else 0
     window, keep = m["mask"]["size"], m["mask"]["keep_first"]
     out = np.zeros((n, H, dv), D64)
     weights = np.zeros((H, n, n), D64)
@@ -88,7 +88,7 @@ def attention(x, w, p, m, eps, v_first=None, return_weights=False):
         g = h // (H // G)
         for i in range(n):
             js = [j for j in range(i + 1) if may_see(i, j, window, keep)]
-            s = np.array([q[i, h] @ k[j, g] * m["scale"] + rel[distance_bucket(i - j, rows, m["bias_max"]), h] for j in js])
+            s = np.array([q[i, h] @ k[j, g] * m["scale"] + (rel[distance_bucket(i - j, rows, m["bias_max"]), h] if rows else 0.0) for j in js])
             e = np.exp(s - s.max())
             a = e / e.sum()
             weights[h, i, js] = a

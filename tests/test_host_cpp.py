@@ -32,6 +32,7 @@ def host_tests(tmp_path_factory):
 
 
 CASES = ["free_list_never_loses_or_doubles", "slots_and_pages_come_back", "groups_with_different_needs_have_their_own_storage",
+         "a_window_group_keeps_the_pages_of_its_first_tokens",
          "arena_plan_packs_by_liveness", "loop_unequal_prompts_stop_tokens_and_early_ends", "loop_runs_batch_after_batch_and_reuses_slots",
          "batches_are_cut_by_pages_and_slots", "loop_closes_slots_when_a_step_fails", "loop_with_queued_decode_runs_gives_the_same_tokens",
          "pretokenizer_pieces", "bpe_round_trip_and_special_ids", "streamer_emits_deltas_and_waits_for_whole_characters",

@@ -173,7 +173,7 @@ const char* vmb_weight_table(const char* config_json) {
 
 int vmb_check_model_folder(const char* folder) {
     return status([&] {
-        const json::Value cfg = read_config_json(folder);
+        const json::Value cfg = read_model_config(folder);
         const std::string where = std::string(folder) + "/config.json";
         DecoderModel model(resolve_architecture(cfg, where)(cfg, where));
         load_weights(folder, model.weight_table());

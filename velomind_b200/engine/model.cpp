@@ -149,29 +149,30 @@ void DecoderModel::forward(StepContext& ctx) {
 
 WeightTable weight_table(const ModelPlan& plan) { return DecoderModel(plan).weight_table(); }
 
+json::Value read_model_config(const std::string& folder) {
+    json::Value data = read_config_json(folder);
+    const std::string path = folder + "/model.safetensors";
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) return data;
+    std::fclose(f);
+    json::Value shapes;
+    shapes.object();
+    for (const auto& kv : load_safetensors(path)) {      // (a mapping of the file: nothing is copied)
+        json::Array extents;
+        for (long long d : kv.second.shape) extents.emplace_back(d);
+        shapes.set(kv.first, json::Value(extents));
+    }
+    data.set("tensor_shapes", shapes);
+    return data;
+}
+
 std::shared_ptr<DecoderModel> load_model(const std::string& folder, DType dtype, const std::string& device) {
     const json::Value data = read_config_json(folder);
     const std::string where = folder + "/config.json";
     const PlanFunction plan_of = resolve_architecture(data, where);
-    // A size that config.json leaves to the checkpoint (the rows of a table) is read from the tensors' shapes: the plan function
-    // finds them under the key `tensor_shapes`, name -> list of extents.
-    const std::string path = folder + "/model.safetensors";
-    HostTensors found;
-    json::Value with_shapes = data;
-    if (FILE* f = std::fopen(path.c_str(), "rb")) {
-        std::fclose(f);
-        found = load_safetensors(path);
-        json::Value shapes;
-        for (const auto& kv : found) {
-            json::Array extents;
-            for (long long d : kv.second.shape) extents.emplace_back(d);
-            shapes.set(kv.first, json::Value(extents));
-        }
-        if (!found.empty()) with_shapes.set("tensor_shapes", shapes);
-    }
-    auto model = std::make_shared<DecoderModel>(plan_of(with_shapes, where));
+    auto model = std::make_shared<DecoderModel>(plan_of(read_model_config(folder), where));
     model->config = data;
-    const HostTensors tensors = found.empty() ? load_weights(folder, model->weight_table()) : check_and_bind(found, model->weight_table(), path);
+    const HostTensors tensors = load_weights(folder, model->weight_table());
     const int dev = require_cuda(device);          // one clear refusal before the first tensor moves: there is no CPU fallback
     cudaStream_t stream = nullptr;
     ops::cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "creating a stream");

@@ -131,6 +131,9 @@ private:
 };
 
 json::Value read_config_json(const std::string& folder_or_file);
+// config.json of a model folder plus, under the key `tensor_shapes` (name -> list of extents), the shapes of the tensors in its
+// model.safetensors, if that file is there: a plan function finds there what config.json leaves to the checkpoint (the rows of a table).
+json::Value read_model_config(const std::string& folder);
 
 // The Llama dense decoder's configuration.  Required keys follow the reference's parser
 // (examples/smollm2/config_parser.cpp:205-213) and its `llama::Config` (examples/common/llama/llama_config.h:7-24).

@@ -92,10 +92,12 @@ ModelPlan semesun_plan(const json::Value& config, const std::string& where) {
             a.set("bias_rows", rows);
             a.set("bias_far", far);
             if (m.boolean_or("v_mix", false)) {
-                const long long values = m.integer("kv_heads") * m.integer("vdim");
+                // (key heads and value size packed into one number: both must be those of the first blending layer)
+                const long long values = m.integer("kv_heads") * (1ll << 32) + m.integer("vdim");
                 if (blend_width < 0) blend_width = values;
                 else if (blend_width != values)
-                    throw ConfigError(format("%s.mixer: v_mix blends values of %lld per token with the first such layer's %lld", lw.c_str(), values, blend_width));
+                    throw ConfigError(format("%s.mixer: v_mix blends this layer's values with the first such layer's: kv_heads and vdim must be equal (%lld x %lld here, %lld x %lld there)",
+                                             lw.c_str(), values >> 32, values & 0xffffffff, blend_width >> 32, blend_width & 0xffffffff));
                 a.set("v_blend", n_blend++ == 0 ? "source" : "blend");
             }
             b.mixer = PartSpec{"window_attention", a};
