@@ -201,7 +201,7 @@ inline void qkv_prepare(void* qkv, int ld, const float* wq, const float* wk, flo
 struct BiasedMask {
     const float* rel = nullptr;         // device float32 [rows, H], or null: no bias
     const int* bucket_of = nullptr;     // device int32 [far + 1]
-    int far = 0, window = 0, keep_first = 0;
+    int far = 0, rows = 0, window = 0, keep_first = 0;
 };
 // attention of the step's tokens over the cache with that mask and bias; keys of Dk, values of Dv; picks the kernel by shape and dtype
 void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int Dk, int Dv, float scale,

@@ -102,6 +102,17 @@ int vm_attention_biased_generic(const void* q, int q_row_stride, const void* kpa
                                 int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int act_dtype,
                                 int* err, cudaStream_t stream);
 
+// ---- attention_biased_fast.cu: the same attention in bfloat16: prompts on mma.sync tiles (keys and values of the sizes that
+// vm_attention_biased_prefill_fits names; n_tiles = sum over the sequences of ceil(new tokens / 64)), decode steps (token s is sequence s's)
+int vm_attention_biased_prefill_fits(int Dk, int Dv);
+int vm_attention_biased_prefill_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
+                                     int max_blocks, const int* positions, const int* cu_tokens, int B, int n_tiles, const float* rel,
+                                     const int* bucket_of, int far, int rel_rows, void* out, int H, int Hkv, int Dk, int Dv, float scale,
+                                     int window, int keep_first, int n_pages, int* err, cudaStream_t stream);
+int vm_attention_biased_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
+                                    int max_blocks, const int* positions, const float* rel, const int* bucket_of, int far, void* out, int B, int H,
+                                    int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int* err, cudaStream_t stream);
+
 // ---- ssm.cu: a selective state-space mixer (short causal convolution, matrix-state recurrence, gated group norm)
 long long vm_ssm_state_floats(int H, int P, int N, int G, int K);
 int vm_ssm_mixer(const void* proj, int ld, const float* taps, const float* conv_bias, const float* dt_bias, const float* A_log, const float* Dskip,

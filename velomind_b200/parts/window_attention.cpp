@@ -107,6 +107,7 @@ public:
             m.rel = static_cast<const float*>(rel_.ptr);
             m.bucket_of = static_cast<const int*>(bucket_of_.ptr);
             m.far = far_;
+            m.rows = rows_;
         }
         m.window = window_;
         m.keep_first = keep_first_;
