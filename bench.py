@@ -270,6 +270,31 @@ def kogilix_config(z):
                        {"type": "mlstm", "mixer": lstm, "mlp": moe}]}
 
 
+# ------------------------------------------------------------------------------------------------ --design semesun
+# The same widths, four layers: window attention + two-matrix feed-forward, Mamba-2 + routed experts, window attention blending the
+# first layer's values + routed experts, Mamba-2 + routed experts; beside it Kogilix (the closest design of this library: layers
+# listed one by one, a recurrent mixer, routed experts) and the Llama decoder at equal width, depth and feed-forward sizes.
+SEMESUN_EXTRA = {
+    "w1024": dict(kv_heads=4, window=1024, keep_first=4, bias_rows=32, bias_max=4096, ssm_heads=32, ssm_vdim=64, ssm_state=128, ssm_groups=1,
+                  identity=2, groups=2, keep=1),
+    "w2048": dict(kv_heads=8, window=1024, keep_first=4, bias_rows=32, bias_max=4096, ssm_heads=64, ssm_vdim=64, ssm_state=128, ssm_groups=1,
+                  identity=2, groups=2, keep=1),
+}
+
+
+def semesun_config(z, x):
+    att = {"heads": z["heads"], "kv_heads": x["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5, "bias_max": x["bias_max"],
+           "bias_rows": x["bias_rows"], "mask": {"size": x["window"], "keep_first": x["keep_first"]}, "v_mix": True}
+    ssm = {"heads": x["ssm_heads"], "vdim": x["ssm_vdim"], "state": x["ssm_state"], "groups": x["ssm_groups"], "conv": 4, "norm_groups": 1}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "identity": x["identity"], "top": z["top"], "scale": 1.0, "groups": {"count": x["groups"], "keep": x["keep"]}}}
+    return {"architecture": "Semesun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": z["ff"]}},
+                       {"type": "mamba2", "mixer": ssm, "mlp": moe},
+                       {"type": "attention", "mixer": att, "mlp": moe},
+                       {"type": "mamba2", "mixer": ssm, "mlp": moe}]}
+
+
 def llama_config_like(z):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 4, "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["heads"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
@@ -290,7 +315,7 @@ def op_table(vm, engine, entries):
 
 
 def design_arm(args):
-    """Prompt and decode throughput of the Kogilix design at a few sizes, beside the Llama decoder at equal size."""
+    """Prompt and decode throughput of a design (Kogilix, Semesun) at a few sizes, beside the library's other models at equal size."""
     import numpy as np
     import velomind_b200 as vm
     T, B, prompt_len = 2048, 8, 512
@@ -300,7 +325,10 @@ def design_arm(args):
     clock.start()
     for name, z in KOGILIX_SIZES.items():
         row = {}
-        for which, cfg in (("kogilix", kogilix_config(z)), ("llama", llama_config_like(z))):
+        models = [("kogilix", kogilix_config(z)), ("llama", llama_config_like(z))]
+        if args.design == "semesun":
+            models.insert(0, ("semesun", semesun_config(z, SEMESUN_EXTRA[name])))
+        for which, cfg in models:
             with tempfile.TemporaryDirectory(prefix="velomind_bench_") as folder:
                 vm.write_random_model(folder, cfg, seed=0, std=0.02)
                 te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="bfloat16", max_tokens=B * 1024 + 4 * T, max_batch=B)).load()
@@ -324,7 +352,7 @@ def design_arm(args):
             del te
         sizes[name] = dict(row, config=z)
     clocks = clock.stop()
-    return {"design": "kogilix", "metric": "prompt tok/s (one prompt of 2,048 tokens, first-seen shape) and decode tok/s (batch 8, 512 cached tokens)",
+    return {"design": args.design, "metric": "prompt tok/s (one prompt of 2,048 tokens, first-seen shape) and decode tok/s (batch 8, 512 cached tokens)",
             "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "layers": 4, "sizes": sizes,
             "clocks": clocks, "peaks": peaks()}
 
@@ -428,7 +456,7 @@ def main() -> int:
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="sizes of the random model: the benchmark's SmolLM2-135M (default), or the 360M / 1.7B shapes of the family")
-    ap.add_argument("--design", default="", choices=["", "kogilix"],
+    ap.add_argument("--design", default="", choices=["", "kogilix", "semesun"],
                     help="instead of the benchmark: prompt and decode throughput of another design of the library at a few layer sizes, "
                          "beside the Llama decoder at equal size (one JSON line of its own)")
     args = ap.parse_args()

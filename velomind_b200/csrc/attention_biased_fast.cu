@@ -242,10 +242,10 @@ int launch_biased_prefill(const void* q, int q_row_stride, const void* kpages, c
 }
 
 // ------------------------------------------------------------------------------------------------ decode steps
-constexpr int DEC_WARPS = 8;
+constexpr int DEC_WARPS = 16;
 
 // token s of the step is sequence s's one new token
-template <int VPL>      // values per lane: ceil(Dv / 32)
+template <int VPL>      // pairs of values per lane: ceil(Dv / 64); lane owns columns 2 lane + 64 i and the next
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
                           const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
@@ -270,10 +270,10 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
     const int first_window_chunk = lo / 32;
     const int n_chunks = kept_chunks + (pos / 32 - first_window_chunk + 1);
     float m = -INFINITY, l = 0.f;
-    float acc[VPL];
+    float acc[VPL][2];
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
-    const bool vec = (Dk % 8) == 0;
+    for (int i = 0; i < VPL; ++i) acc[i][0] = acc[i][1] = 0.f;
+    const bool vec = (Dk % 8) == 0, pairs = (Dv % 2) == 0;
     for (int c = warp; c < n_chunks; c += DEC_WARPS) {
         const int base = (c < kept_chunks ? c : first_window_chunk + (c - kept_chunks)) * 32;
         const int blk = base / VM_PAGE_TOKENS;
@@ -290,7 +290,8 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
             const __nv_bfloat16* krow = kpages + (tok0 + lane) * Dk;
             float a = 0.f;
             if (vec) {
-                for (int d = 0; d < Dk; d += 8) {
+#pragma unroll 4
+                for (int d = 0; d < Dk; d += 8) {         // (unrolled: the row's 16-byte loads are in flight together)
                     const uint4 u = *reinterpret_cast<const uint4*>(krow + d);
                     const unsigned w4[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -312,16 +313,25 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
         const float alpha = expf(m - m_new);
         l = l * alpha + vm_warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) acc[i] *= alpha;
+        for (int i = 0; i < VPL; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
         const int cnt = min(32, pos - base + 1);
-        for (int jj = 0; jj < cnt; ++jj) {
+#pragma unroll 8
+        for (int jj = 0; jj < cnt; ++jj) {                 // (no branch inside: the rows' loads overlap; a key that is not seen has p = 0)
             const float pj = __shfl_sync(0xffffffffu, p, jj);
-            if (pj == 0.f) continue;
             const __nv_bfloat16* vrow = vpages + (tok0 + jj) * Dv;
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
-                const int d = lane + 32 * i;
-                if (d < Dv) acc[i] = fmaf(pj, __bfloat162float(vrow[d]), acc[i]);
+                const int d = 2 * lane + 64 * i;
+                if (pairs) {
+                    if (d < Dv) {
+                        const float2 v2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + d));
+                        acc[i][0] = fmaf(pj, v2.x, acc[i][0]);
+                        acc[i][1] = fmaf(pj, v2.y, acc[i][1]);
+                    }
+                } else {
+                    if (d < Dv) acc[i][0] = fmaf(pj, __bfloat162float(vrow[d]), acc[i][0]);
+                    if (d + 1 < Dv) acc[i][1] = fmaf(pj, __bfloat162float(vrow[d + 1]), acc[i][1]);
+                }
             }
         }
         m = m_new;
@@ -330,24 +340,25 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
     if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < Dv) mine[2 + d] = acc[i];
+        const int d = 2 * lane + 64 * i;
+        if (d < Dv) mine[2 + d] = acc[i][0];
+        if (d + 1 < Dv) mine[2 + d + 1] = acc[i][1];
     }
     __syncthreads();
     if (warp != 0) return;
     float M = -INFINITY;
     for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, part[(size_t)w * (Dv + 2)]);
     float L = 0.f;
-    float res[VPL];
+    float res[2 * VPL];
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) res[i] = 0.f;
+    for (int i = 0; i < 2 * VPL; ++i) res[i] = 0.f;
     for (int w = 0; w < DEC_WARPS; ++w) {                   // in warp order: the same sum whatever else runs
         const float* pw = part + (size_t)w * (Dv + 2);
         if (pw[0] == -INFINITY) continue;
         const float f = expf(pw[0] - M);
         L = fmaf(pw[1], f, L);
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) {
+        for (int i = 0; i < 2 * VPL; ++i) {
             const int d = lane + 32 * i;
             if (d < Dv) res[i] = fmaf(pw[2 + d], f, res[i]);
         }
@@ -355,7 +366,7 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
     const float inv = 1.0f / L;
     __nv_bfloat16* orow = out + ((size_t)seq * H + h) * Dv;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
+    for (int i = 0; i < 2 * VPL; ++i) {
         const int d = lane + 32 * i;
         if (d < Dv) orow[d] = __float2bfloat16_rn(res[i] * inv);
     }
@@ -407,8 +418,8 @@ VM_API int vm_attention_biased_decode_bf16(const void* q, int q_row_stride, cons
                           (const __nv_bfloat16*)kpages, (const __nv_bfloat16*)vpages, block_table, max_blocks, positions, rel, bucket_of, far, \
                           (__nv_bfloat16*)out, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, err);                                      \
         break;
-    switch ((Dv + 31) / 32) {
-        VM_BD(1) VM_BD(2) VM_BD(3) VM_BD(4) VM_BD(5) VM_BD(6) VM_BD(7) VM_BD(8)
+    switch ((Dv + 63) / 64) {
+        VM_BD(1) VM_BD(2) VM_BD(3) VM_BD(4)
         default: return VM_ERR_UNSUPPORTED;
     }
 #undef VM_BD

@@ -208,6 +208,7 @@ void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const K
                       const BiasedMask& mask);
 
 // the state-space mixer's kernels over the running schedule position's state area
+constexpr int SSM_CHUNKS_FROM_TOKENS = 64;      // a step's capacity from which prompts run chunk by chunk
 inline void ssm_mixer(const void* proj, int ld, const float* taps, const float* conv_bias, const float* dt_bias, const float* A_log, const float* Dskip,
                       const float* norm_w, float eps, StepContext& ctx, void* out, int H, int P, int N, int G, int K, int parts) {
     Timed t("ssm_mixer", ctx.stream);
@@ -215,10 +216,21 @@ inline void ssm_mixer(const void* proj, int ld, const float* taps, const float* 
     const long long C = static_cast<long long>(H) * P + 2ll * G * N;
     void* xbc = ctx.take_tokens(C, ctx.act_dtype);
     float* y = static_cast<float*>(ctx.take_tokens(static_cast<long long>(H) * P, DType::F32));
+    // The choice follows the step's capacity bucket alone, so that every step of a bucket asks for the same scratch: decode steps and
+    // the smallest pieces go token by token, everything else chunk by chunk (every sequence may end in a chunk that is not full).
+    const bool chunks = !ctx.one_token_each && ctx.T_cap >= SSM_CHUNKS_FROM_TOKENS && P <= 128;
+    float* scratch = nullptr;
+    int n_chunks = 0;
+    if (chunks) {
+        scratch = static_cast<float*>(ctx.take(vm_ssm_chunk_scratch_floats(ctx.T_cap, ctx.T_cap / 64 + ctx.B_cap, H, P, N), DType::F32));
+        for (int b = 0; b < ctx.B; ++b) n_chunks += (ctx.host_cu_tokens[b + 1] - ctx.host_cu_tokens[b] + 63) / 64;
+    }
     check(vm_ssm_mixer(proj, ld, taps, conv_bias, dt_bias, A_log, Dskip, norm_w, eps, ctx.state(), ctx.state_floats(), ctx.positions, ctx.seq_of_token,
-                       ctx.cu_tokens, ctx.slots, xbc, y, out, ctx.T, ctx.B, H, P, N, G, K, parts, code(ctx.act_dtype), ctx.stream),
+                       ctx.cu_tokens, ctx.slots, xbc, y, out, scratch, n_chunks, ctx.one_token_each ? 1 : 0, ctx.T, ctx.B, H, P, N, G, K, parts,
+                       code(ctx.act_dtype), ctx.stream),
           "ssm_mixer", ctx.stream);
-    counters().own_launches += K > 1 ? 3 : 2;      // four kernels
+    counters().own_launches += ctx.one_token_each ? 2 : (chunks ? 5 : (K > 1 ? 3 : 2));
+    ctx.give(scratch);
     ctx.give(y);
     ctx.give(xbc);
 }

@@ -115,10 +115,12 @@ int vm_attention_biased_decode_bf16(const void* q, int q_row_stride, const void*
 
 // ---- ssm.cu: a selective state-space mixer (short causal convolution, matrix-state recurrence, gated group norm)
 long long vm_ssm_state_floats(int H, int P, int N, int G, int K);
+long long vm_ssm_chunk_scratch_floats(int T, int n_chunks, int H, int P, int N);
+// chunk_scratch given with n_chunks = sum over the sequences of ceil(new tokens / 64): prompts run chunk by chunk; one_token_each: decode steps
 int vm_ssm_mixer(const void* proj, int ld, const float* taps, const float* conv_bias, const float* dt_bias, const float* A_log, const float* Dskip,
                  const float* norm_w, float eps, float* state, int state_floats, const int* positions, const int* seq_of_token, const int* cu_tokens,
-                 const int* slots, void* xbc, float* y, void* out, int T, int B, int H, int P, int N, int G, int K, int parts, int act_dtype,
-                 cudaStream_t stream);
+                 const int* slots, void* xbc, float* y, void* out, float* chunk_scratch, int n_chunks, int one_token_each, int T, int B, int H, int P,
+                 int N, int G, int K, int parts, int act_dtype, cudaStream_t stream);
 
 // ---- rope_cache.cu
 int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
