@@ -74,6 +74,8 @@ MECHANISMS = {
     "attention_tiles": ("mixer", "window_attention", attention_args(128, 4, 2, 64, 32, 0.15, 50, 3, 16, 240)),
     "attention_tiles_kept_page": ("mixer", "window_attention", attention_args(96, 2, 1, 96, 128, 0.1, 100, 70, 10, 90)),
     "attention_tiles_plain": ("mixer", "window_attention", attention_args(64, 4, 4, 32, 16, 0.2, 20, 0, 0, 0)),
+    # a table that reaches further than the distances the tensor-core kernel keeps in shared memory: two look-ups per score
+    "attention_tiles_far_table": ("mixer", "window_attention", attention_args(64, 2, 1, 32, 32, 0.2, 90, 6, 24, 20000)),
     "mamba2": ("mixer", "mamba2", {"hidden": 72, "heads": 3, "vdim": 20, "state": 24, "groups": 1, "conv": 4, "norm_groups": 1, "eps": 1e-5}),
     # two groups, a state that is no multiple of 16, two taps, the norm in four parts
     "mamba2_groups": ("mixer", "mamba2", {"hidden": 64, "heads": 4, "vdim": 12, "state": 21, "groups": 2, "conv": 2, "norm_groups": 4, "eps": 1e-6}),

@@ -22,6 +22,7 @@ struct SkinnyParams {
     int out_stride;
     float* h;                    // residual [M, N]
     int I;                       // swiglu: rows of Wg (and of Wu)
+    int store_act;               // bf16 store: 0, or 1 + the activation (VM_ACT_*) applied to the rounded product
     int gate_act;                // swiglu: the activation of the gate (VM_ACT_SILU = 0, VM_ACT_GELU_TANH, VM_ACT_RELU_SQUARED)
     // rope_kv
     const int* positions; const int* seq_of_token; const int* block_table; int max_blocks;
@@ -262,6 +263,10 @@ __device__ __forceinline__ void skinny_run(const SkinnyParams& p, const int firs
         switch (p.epi) {
             case EPI_STORE_BF16: {
                 __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride;
+                if (p.store_act) {       // the activation of what the product's bfloat16 result would hold, as the unfused step computes it
+                    vA = skinny_gate(__bfloat162float(__float2bfloat16_rn(vA)), p.store_act - 1);
+                    vB = skinny_gate(__bfloat162float(__float2bfloat16_rn(vB)), p.store_act - 1);
+                }
                 o[nA + c] = __float2bfloat16_rn(vA);
                 if (two) o[nB + c] = __float2bfloat16_rn(vB);
             } break;

@@ -178,6 +178,18 @@ VM_API int vm_skinny_linear(const void* A, int pro, const float* norm_w, float e
     return skinny_dispatch(p, items, stream);
 }
 
+// out[M, N] = act(x W^T) in bfloat16, the activation (VM_ACT_*) applied to the product as bfloat16 holds it
+VM_API int vm_skinny_linear_act(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K, int act, void* out,
+                                int out_stride, int* err, cudaStream_t stream) {
+    if (N % 8 != 0 || act < VM_ACT_SILU || act > VM_ACT_RELU_SQUARED) return VM_ERR_UNSUPPORTED;
+    SkinnyParams p{};
+    p.err = err;
+    p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K;
+    p.out = out; p.out_stride = out_stride; p.epi = EPI_STORE_BF16; p.store_act = act + 1;
+    p.tiles = (N % 16 == 0 && N / 16 >= 148) ? 2 : 1;
+    return skinny_dispatch(p, p.tiles == 2 ? N / 16 : N / 8, stream);
+}
+
 // out[M, I] = act(x Wg^T) * (x Wu^T) with x = A (pro 0) or rmsnorm(h) (pro 1); W = [Wg; Wu] is [2I, K]; act is VM_ACT_*.
 VM_API int vm_skinny_gated(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, int act,
                            void* out, int* err, cudaStream_t stream) {

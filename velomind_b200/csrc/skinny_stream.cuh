@@ -283,6 +283,10 @@ skinny_stream_kernel(const SkinnyParams p) {
                 switch (p.epi) {
                     case EPI_STORE_BF16: {
                         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride;
+                        if (p.store_act) {
+                            vA = skinny_gate(__bfloat162float(__float2bfloat16_rn(vA)), p.store_act - 1);
+                            vB = skinny_gate(__bfloat162float(__float2bfloat16_rn(vB)), p.store_act - 1);
+                        }
                         o[nA + c] = __float2bfloat16_rn(vA);
                         if (two) o[nB + c] = __float2bfloat16_rn(vB);
                     } break;

@@ -297,6 +297,13 @@ inline void skinny_linear(const void* x, const float* norm_w, float eps, const D
           "skinny_linear", s);
 }
 
+inline void skinny_linear_act(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, int act, void* out, int out_stride, int* err,
+                              cudaStream_t s) {
+    Timed t("skinny_linear_act", s);
+    check(vm_skinny_linear_act(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, static_cast<int>(W.rows()), static_cast<int>(W.cols()), act, out, out_stride, err, s),
+          "skinny_linear_act", s);
+}
+
 inline void skinny_swiglu(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, int I, void* out, int* err, cudaStream_t s) {
     Timed t("skinny_swiglu", s);
     check(vm_skinny_swiglu(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, I, static_cast<int>(W.cols()), out, err, s), "skinny_swiglu", s);

@@ -170,6 +170,9 @@ int vm_experts_grouped_tc(const void* x, const void* w_up, const void* w_down, c
 // (err: the step's error word, may be null; the kernel for large weight matrices reports a wait that ran out there)
 int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K, void* out,
                      int out_stride, int out_f32, float* residual_h, int* err, cudaStream_t stream);
+// out[M, N] = act(A W^T) in bfloat16: the activation (VM_ACT_*) of the product as bfloat16 holds it (the first half of a two-matrix unit)
+int vm_skinny_linear_act(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K, int act, void* out,
+                         int out_stride, int* err, cudaStream_t stream);
 int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, void* out,
                      int* err, cudaStream_t stream);
 int vm_skinny_gated(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, int act, void* out,

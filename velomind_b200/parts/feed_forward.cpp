@@ -136,16 +136,20 @@ public:
         norm.as_rms(&nw, &eps);
         const bool skinny = ctx.T_cap <= max_rows();
         void* u = ctx.take_tokens(I_, DType::BF16);
+        // (few tokens: the activation rides in the first product's epilogue)
         if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
-            ops::skinny_linear(h, nw, eps, up_.weight, ctx.T, u, I_, false, nullptr, ctx.err, ctx.stream);
+            ops::skinny_linear_act(h, nw, eps, up_.weight, ctx.T, act_, u, I_, ctx.err, ctx.stream);
         } else {
             void* x = ctx.take_tokens(hidden_, DType::BF16);
             norm.forward(ctx, h, nullptr, x, nullptr, 0);
-            if (skinny) ops::skinny_linear(x, nullptr, 0.f, up_.weight, ctx.T, u, I_, false, nullptr, ctx.err, ctx.stream);
-            else ops::linear(x, DType::BF16, hidden_, up_.weight, u, DType::BF16, ctx.T, ctx.stream);
+            if (skinny) {
+                ops::skinny_linear_act(x, nullptr, 0.f, up_.weight, ctx.T, act_, u, I_, ctx.err, ctx.stream);
+            } else {
+                ops::linear(x, DType::BF16, hidden_, up_.weight, u, DType::BF16, ctx.T, ctx.stream);
+                ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, DType::BF16, ctx.stream);
+            }
             ctx.give(x);
         }
-        ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, DType::BF16, ctx.stream);
         if (skinny) ops::skinny_linear(u, nullptr, 0.f, down_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         else ops::linear_residual(u, I_, down_.weight, h, ctx.T, ctx.stream);
         ctx.give(u);
