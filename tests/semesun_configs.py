@@ -41,13 +41,13 @@ SEM_A = {
 
 # sizes the tensor-core kernels and the vector loads accept; attention first; several layers in one cache group
 SEM_B = {
-    "architecture": "Semesun", "vocab": 320, "width": 192, "norm": {"eps": 1e-6},
+    "architecture": "Semesun", "vocab": 320, "width": 256, "norm": {"eps": 1e-6},
     "layers": [
-        {"type": "attention", "mixer": attention(4, 2, 64, 32, 0.14, 96, 5, 300, 16), "mlp": moe(8, 0, 2, 64, 1.5, 2, 1, 1.0)},
-        {"type": "mamba2", "mixer": ssm(6, 32, 64, 2, 4, 2), "mlp": dense(256)},
-        {"type": "attention", "mixer": attention(4, 2, 64, 32, 0.14, 96, 5, 300, 16), "mlp": moe(6, 2, 3, 64, 1.0, 4, 3, 2.0)},
-        {"type": "attention", "mixer": attention(8, 2, 32, 32, 0.2, 40, 0, 50, 8), "mlp": dense(128)},
-        {"type": "attention", "mixer": attention(4, 2, 64, 32, 0.14, 96, 5, 300, 16), "mlp": dense(64)},
+        {"type": "attention", "mixer": attention(8, 2, 32, 64, 0.17, 96, 5, 300, 12), "mlp": moe(8, 0, 2, 96, 1.25, 2, 1, 1.0)},
+        {"type": "mamba2", "mixer": ssm(6, 32, 64, 2, 4, 2), "mlp": dense(384)},
+        {"type": "attention", "mixer": attention(8, 2, 32, 64, 0.17, 96, 5, 300, 12), "mlp": moe(6, 2, 3, 64, 1.0, 4, 3, 2.0)},
+        {"type": "attention", "mixer": attention(4, 2, 64, 64, 0.2, 40, 0, 50, 8), "mlp": dense(128)},
+        {"type": "attention", "mixer": attention(8, 2, 32, 64, 0.17, 96, 5, 300, 12), "mlp": dense(64)},
     ],
 }
 

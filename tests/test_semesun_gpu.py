@@ -25,7 +25,7 @@ def attention_args(hidden, heads, kv_heads, dim, vdim, scale, window, keep_first
             "keep_first": keep_first, "bias_rows": rows, "bias_far": far, "eps": eps}
 
 
-def as_card(args):
+def as_config(args):
     """A part's arguments in the shape the plain functions take (the configuration's own)."""
     return {"heads": args["heads"], "kv_heads": args["kv_heads"], "dim": args["dim"], "vdim": args["vdim"], "scale": args["scale"],
             "bias_max": args["bias_far"], "mask": {"size": args["window"] if args["window"] else 10 ** 9, "keep_first": args["keep_first"]}}
@@ -36,7 +36,7 @@ def moe_args(hidden, experts, identity, top, ff, limit, groups, keep, scale):
             "groups_keep": keep, "scale": scale, "glu": 1, "limit": limit, "alpha": 1.702}
 
 
-def moe_as_card(a):
+def moe_as_config(a):
     return {"kind": "moe", "expert": {"ff": a["ff"], "limit": a["limit"]},
             "router": {"experts": a["experts"], "identity": a["identity"], "top": a["top"], "scale": a["scale"],
                        "groups": {"count": a["groups"], "keep": a["groups_keep"]}}}
@@ -71,7 +71,7 @@ MECHANISMS = {
     "attention_wide": ("mixer", "window_attention", attention_args(64, 2, 1, 32, 32, 0.2, 1000, 2, 6, 20)),
     # sizes the tensor-core kernel of prompts takes (bfloat16): keys of 64 and values of 32; keys of 96 and values of 128 with more
     # kept tokens than a page; keys of 32 and values of 16 without a table
-    "attention_tiles": ("mixer", "window_attention", attention_args(128, 4, 2, 64, 32, 0.15, 50, 3, 16, 240)),
+    "attention_tiles": ("mixer", "window_attention", attention_args(128, 4, 1, 64, 32, 0.15, 50, 3, 18, 260)),
     "attention_tiles_kept_page": ("mixer", "window_attention", attention_args(96, 2, 1, 96, 128, 0.1, 100, 70, 10, 90)),
     "attention_tiles_plain": ("mixer", "window_attention", attention_args(64, 4, 4, 32, 16, 0.2, 20, 0, 0, 0)),
     # a table that reaches further than the distances the tensor-core kernel keeps in shared memory: two look-ups per score
@@ -96,12 +96,12 @@ MECHANISMS = {
 def plain_mechanism(name, args, x, w):
     kind = MECHANISMS[name][1]
     if kind == "window_attention":
-        return P.attention(x, w, MIX, as_card(args), args["eps"])
+        return P.attention(x, w, MIX, as_config(args), args["eps"])
     if kind == "mamba2":
         return P.mamba2(x, w, MIX, args, args["eps"])
     if kind == "mlp":
         return P.dense(x, w, FF)
-    return P.routed_experts(x, w, FF, moe_as_card(args))
+    return P.routed_experts(x, w, FF, moe_as_config(args))
 
 
 def shape_weights(kind, w, rng):
@@ -147,7 +147,7 @@ def test_each_mechanism_alone(name, dtype, toy_plugin, tmp_path):
         plain[rid] = x + plain_mechanism(name, args, x, w)
     if kind == "routed_experts":        # the test sees a wrong expert only if the routing spreads, identity experts included
         x = w["embed.weight"].astype(np.float64)
-        chosen = P.route(x, w, FF, moe_as_card(args)["router"])[0]
+        chosen = P.route(x, w, FF, moe_as_config(args)["router"])[0]
         assert len(set(chosen.reshape(-1).tolist())) == args["experts"] + args["identity"]
     cuts = standard_cuts(requests)
     cuts["pieces"] = steps_in_pieces(requests, (2, 3, 64, 1, 65))
@@ -168,7 +168,7 @@ def test_an_excluded_group_counts_as_minus_infinity():
     a = moe_args(32, 6, 0, 2, 8, 1.0, 3, 1, 1.0)
     w = {FF + "router": rng.normal(0, 1, (6, 32)), FF + "correction": np.full(6, -3.0)}
     x = rng.normal(0, 1, (200, 32))
-    chosen, weights = P.route(x, w, FF, moe_as_card(a)["router"])
+    chosen, weights = P.route(x, w, FF, moe_as_config(a)["router"])
     assert ((chosen[:, 0] // 2) == (chosen[:, 1] // 2)).all()      # both from the one group that stays
     assert len(set((chosen[:, 0] // 2).tolist())) == 3 and (weights > 0).all()
 
@@ -187,14 +187,14 @@ def test_routing_on_the_gpu_with_negative_scores_and_ties(toy_plugin, tmp_path):
     w[FF + "router"][8] = w[FF + "router"][7]          # and between an expert's neighbour and an identity expert
     w = rounded_to_bf16(w)
     requests = S.make_requests(64, (150, 4), seed=5)
-    chosen = P.route(w["embed.weight"].astype(np.float64), w, FF, moe_as_card(args)["router"])[0]
+    chosen = P.route(w["embed.weight"].astype(np.float64), w, FF, moe_as_config(args)["router"])[0]
     assert ((chosen // 3).min(axis=1) == (chosen // 3).max(axis=1)).all() and len(set((chosen // 3).reshape(-1).tolist())) == 3
     assert (chosen == 3).any() and ((chosen == 3).sum(axis=1) >= (chosen == 4).sum(axis=1)).all()
     assert (chosen >= 7).any()
     plain = {}
     for rid, toks in requests.items():
         x = w["embed.weight"].astype(np.float64)[toks]
-        plain[rid] = x + P.routed_experts(x, w, FF, moe_as_card(args))
+        plain[rid] = x + P.routed_experts(x, w, FF, moe_as_config(args))
     for dtype, tol, as_bf16 in (("float32", 3e-5, False), ("bfloat16", 2e-2, True)):
         folder = write_model(str(tmp_path / dtype), cfg, w, as_bf16=as_bf16)
         engine = vm.Engine(vm.load_model(folder, dtype, "cuda:0"), 64 * 4)
@@ -215,7 +215,7 @@ def test_experts_of_many_tokens_bfloat16(toy_plugin, tmp_path):
     plain = {}
     for rid, toks in requests.items():
         x = w["embed.weight"].astype(np.float64)[toks]
-        plain[rid] = x + P.routed_experts(x, w, FF, moe_as_card(args))
+        plain[rid] = x + P.routed_experts(x, w, FF, moe_as_config(args))
     cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests, tail=20), "batches": S.steps_unequal_batches(requests)}
     run_cuts(engine, requests, plain, cuts, 2.5e-2)
 
@@ -258,7 +258,7 @@ def test_a_key_decides_where_the_mask_lets_it(place, seen, dims, toy_plugin, tmp
     toks[place] = key
     toks[-1] = ask
     x = w["embed.weight"].astype(np.float64)[toks]
-    y, weights = P.attention(x, w, MIX, as_card(args), args["eps"], return_weights=True)
+    y, weights = P.attention(x, w, MIX, as_config(args), args["eps"], return_weights=True)
     if seen:
         assert weights[:, -1, place].min() > 0.9          # the crafted key really carries the answer
     else:
@@ -291,7 +291,7 @@ def test_the_window_passes_over_decoded_tokens(toy_plugin, tmp_path):
     for at in (230, 269, 270, 271, 329):                   # 269 is the last place that sees 200
         toks[at] = ask
     x = w["embed.weight"].astype(np.float64)[toks]
-    y, weights = P.attention(x, w, MIX, as_card(args), args["eps"], return_weights=True)
+    y, weights = P.attention(x, w, MIX, as_config(args), args["eps"], return_weights=True)
     assert weights[:, 269, 200].min() > 0.3 and weights[:, 270, 200].max() == 0.0 and weights[:, 329, 1].min() > 0.9
     plain = {"r": x + y}
     requests = {"r": toks}
