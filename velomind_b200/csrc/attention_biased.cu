@@ -28,6 +28,8 @@ __global__ void qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __r
                                    int max_blocks, T* __restrict__ kpages, T* __restrict__ vpages, int H, int Hkv, int Dk, int Dv, int n_pages,
                                    int* __restrict__ err) {
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int pos = positions[t], seq = seq_of_token[t];
     const int blk = pos / VM_PAGE_TOKENS, in_page = pos % VM_PAGE_TOKENS;
     int page = -1;
@@ -181,13 +183,12 @@ VM_API int vm_qkv_prepare(void* qkv, int ld, const float* wq, const float* wk, f
     if (H <= 0 || Hkv <= 0 || Dk <= 0 || Dv <= 0 || ld < (H + Hkv) * Dk + Hkv * Dv) return VM_ERR_BAD_ARG;
     if ((v_first != nullptr) != (lambda != nullptr)) return VM_ERR_BAD_ARG;
     if (act_dtype == VM_F32)
-        qkv_prepare_kernel<float><<<T, PREP_WARPS * 32, 0, stream>>>((float*)qkv, ld, wq, wk, eps, lambda, (const float*)v_first, (float*)v_keep, positions,
-                                                                     seq_of_token, block_table, max_blocks, (float*)kpages, (float*)vpages, H, Hkv, Dk,
-                                                                     Dv, n_pages, err);
+        vm_launch_pdl(qkv_prepare_kernel<float>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (float*)qkv, ld, wq, wk, eps, lambda, (const float*)v_first,
+                      (float*)v_keep, positions, seq_of_token, block_table, max_blocks, (float*)kpages, (float*)vpages, H, Hkv, Dk, Dv, n_pages, err);
     else if (act_dtype == VM_BF16)
-        qkv_prepare_kernel<__nv_bfloat16><<<T, PREP_WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, ld, wq, wk, eps, lambda, (const __nv_bfloat16*)v_first,
-                                                                             (__nv_bfloat16*)v_keep, positions, seq_of_token, block_table, max_blocks,
-                                                                             (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, H, Hkv, Dk, Dv, n_pages, err);
+        vm_launch_pdl(qkv_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, ld, wq, wk, eps, lambda,
+                      (const __nv_bfloat16*)v_first, (__nv_bfloat16*)v_keep, positions, seq_of_token, block_table, max_blocks, (__nv_bfloat16*)kpages,
+                      (__nv_bfloat16*)vpages, H, Hkv, Dk, Dv, n_pages, err);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
 }

@@ -92,6 +92,8 @@ __global__ void ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __res
                                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, float* __restrict__ y, int H, int P, int N, int G,
                                 int PB) {
     extern __shared__ float sm[];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PB;
     const int g = h / (H / G);
     const int n_slices = (N + NPT - 1) / NPT;
@@ -466,6 +468,8 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
                                         int inner, int parts, T* __restrict__ out) {
     extern __shared__ float gs[];                          // [inner]
     __shared__ float red[32];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int t = blockIdx.x;
     const int per = inner / parts;
     for (int i = threadIdx.x; i < inner; i += blockDim.x) gs[i] = y[(size_t)t * inner + i] * silu_f(vm_to_float(proj[(size_t)t * ld + z_col + i]));
@@ -500,8 +504,8 @@ int launch_scan(const void* xbc, int C, const void* proj, int ld, int dt_col, co
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     const dim3 grid(B, H, (P + PB - 1) / PB);
 #define VM_SCAN(NPT)                                                                                                                             \
-    ssm_scan_kernel<T, NPT><<<grid, threads, smem, stream>>>((const T*)xbc, C, (const T*)proj, ld, dt_col, dt_bias, A_log, Dskip, state, state_floats, \
-                                                             cu_tokens, slots, y, H, P, N, G, PB)
+    vm_launch_pdl(ssm_scan_kernel<T, NPT>, grid, dim3(threads), smem, stream, (const T*)xbc, C, (const T*)proj, ld, dt_col, dt_bias, A_log, Dskip, state, \
+                  state_floats, cu_tokens, slots, y, H, P, N, G, PB)
     if (npt == 16) VM_SCAN(16);
     else if (npt == 32) VM_SCAN(32);
     else VM_SCAN(64);
@@ -537,7 +541,8 @@ int launch_mixer(const void* proj, int ld, const float* taps, const float* conv_
     else
         st = launch_scan<T>(xbc, C, proj, ld, dt_col, dt_bias, A_log, Dskip, state, state_floats, cu_tokens, slots, y, B, H, P, N, G, vm_sm_count(), stream);
     if (st) return st;
-    gated_group_norm_kernel<T><<<T_, 256, (size_t)inner * sizeof(float), stream>>>(y, (const T*)proj, ld, 0, norm_w, eps, inner, parts, (T*)out);
+    vm_launch_pdl(gated_group_norm_kernel<T>, dim3(T_), dim3(256), (size_t)inner * sizeof(float), stream, (const float*)y, (const T*)proj, ld, 0, norm_w, eps,
+                  inner, parts, (T*)out);
     return vm_launch_status();
 }
 
