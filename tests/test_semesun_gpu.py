@@ -398,13 +398,14 @@ def test_blending_reaches_the_answer(sem_folders):
     assert np.abs(P.forward_logits(cfg, w2, toks) - with_blend).max() > 1e-2 * np.abs(with_blend).max()
 
 
-def test_whole_model_bfloat16(sem_folders, tmp_path):
+@pytest.mark.parametrize("which", ["a", "b"])      # sizes that only the plain kernels take; sizes the tensor-core kernels take
+def test_whole_model_bfloat16(which, sem_folders, tmp_path):
     """The serving precision: weights rounded to bfloat16, then compared with the plain implementation on the SAME rounded
     weights.  A routed layer would choose another expert for a token whose two choice scores are closer than the rounding of
     its input, and the answer would then differ by more than rounding; so here every routed layer takes ALL its outputs (their
     weights are still the scores), and the choice itself is left to the float32 tests."""
     import velomind_b200 as vm
-    cfg, w = P.read_model(sem_folders["b"])
+    cfg, w = P.read_model(sem_folders[which])
     for layer in cfg["layers"]:
         if layer["mlp"] and layer["mlp"]["kind"] == "moe":
             r = layer["mlp"]["router"]
